@@ -398,8 +398,31 @@ def zaparax_config(hf: Dict[str, Any]) -> Dict[str, Any]:
                 hybrid={"layers": layers, "loop": hf.get("loop") or None, "embedding": hf.get("embedding") or {}})
 
 
+def resatar_config(hf: Dict[str, Any]) -> Dict[str, Any]:
+    """Resatar ``config.json`` -> ModelConfig fields.  ``layers[i]`` = ``type`` of the mixer (``attention`` | ``parallel`` | ``mamba1``), its sizes
+    and constants under ``mixer`` (a parallel mixer: ``left`` / ``right`` with ``left_scale`` / ``right_scale``), the feed-forward under ``mlp``
+    (``kind`` ``dense`` | ``moe``) or null; globals ``width``, ``vocab``, ``norm.eps``.  The flat fields are summaries for code that sizes
+    buffers; the model reads ``hybrid``."""
+    layers = [dict(l) for l in hf["layers"]]
+    width = int(hf["width"])
+    mlps = [l["mlp"] for l in layers if l.get("mlp")]
+    moes = [m for m in mlps if m.get("kind") == "moe"]
+    ffs = [int(m["ff"]) if m.get("kind") == "dense" else int(m["expert"]["ff"]) * int(m["router"]["top"]) + int((m.get("shared") or {}).get("ff", 0))
+           for m in mlps]
+    attn = [l["mixer"] for l in layers if l["type"] == "attention"] + [l["mixer"]["left"] for l in layers if l["type"] == "parallel"]
+    heads = max([int(m["heads"]) for m in attn] or [1])
+    return dict(architecture="Resatar", hidden_size=width, vocab_size=int(hf["vocab"]), num_hidden_layers=len(layers),
+                rms_norm_eps=float((hf.get("norm") or {}).get("eps", 1e-6)), final_logit_softcapping=0.0,
+                num_attention_heads=heads, num_key_value_heads=1, head_dim=max([int(m["dim"]) for m in attn] or [width // heads]),
+                intermediate_size=max(ffs or [width]), num_local_experts=max([int(m["router"]["experts"]) for m in moes] or [0]),
+                num_experts_per_tok=max([int(m["router"]["top"]) for m in moes] or [0]),
+                max_position_embeddings=int(hf.get("max_positions") or (1 << 20)), tie_word_embeddings=False, eos_token_id=None,
+                dtype={"float16": "float16", "float32": "float32"}.get(hf.get("dtype") or "bfloat16", "bfloat16"),
+                hybrid={"layers": layers})
+
+
 # configurations that list their layers one by one, chosen by the file's ``architecture`` key
-_LAYER_LIST_READERS = {"Rirotar": rirotar_config, "Zaparax": zaparax_config}
+_LAYER_LIST_READERS = {"Rirotar": rirotar_config, "Zaparax": zaparax_config, "Resatar": resatar_config}
 
 
 def _has_native_class(arch: str) -> bool:

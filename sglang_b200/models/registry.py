@@ -148,6 +148,9 @@ def _register_builtins() -> None:
     from . import zaparax as _zp
 
     register_model("Zaparax", _zp.ZaparaxForCausalLM)
+    from . import resatar as _rs
+
+    register_model("Resatar", _rs.ResatarForCausalLM)
     from . import transformers_fallback as _tff
 
     register_model("TransformersForCausalLM", _tff.TransformersForCausalLM)

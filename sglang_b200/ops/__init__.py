@@ -454,17 +454,17 @@ def add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], weigh
                     out_dtype: torch.dtype = torch.bfloat16, post_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 residual stream: ``residual += delta`` (in place, fp32 sum) and the RMS norm of the new residual in ``out_dtype``, one kernel
     (csrc/kernels/residual_f32.cu).  ``zero_centred``: the weight is stored around zero and applied as ``1 + w``.  ``post_weight``: the branch
-    output is itself RMS-normed, times ``1 + post_weight``, before it joins the residual (sandwich-norm blocks), in the same kernel."""
+    output is itself RMS-normed, times ``1 + post_weight`` (``post_weight`` when not ``zero_centred``), before it joins the residual
+    (sandwich-norm blocks), in the same kernel.  A weight of one element is one gain for all coordinates."""
     if post_weight is not None and delta is not None:
-        assert zero_centred
         if _use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) \
                 and delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous() and weight.dtype == out_dtype and post_weight.dtype == out_dtype:
             out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
-            torch.ops.sglb.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, out, float(eps))
+            torch.ops.sglb.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, out, float(eps), bool(zero_centred))
             return out
-        return torch_ref.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, eps, out_dtype)
+        return torch_ref.postnorm_add_rmsnorm_f32(residual, delta, post_weight, weight, eps, out_dtype, zero_centred)
     if _use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) \
-            and (delta is None or (delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous())):
+            and weight.dtype == out_dtype and (delta is None or (delta.dtype in (torch.bfloat16, torch.float32) and delta.is_contiguous())):
         out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
         torch.ops.sglb.add_rmsnorm_f32(residual, delta, weight, out, float(eps), bool(zero_centred))
         return out
@@ -544,29 +544,44 @@ def bigram_embedding(embed: torch.Tensor, bigram: Optional[torch.Tensor], ids: t
     return torch_ref.bigram_embedding(embed, bigram, ids, prev_tokens, cu_q, req_slots, seq_lens, scale, mul_prev, mul_cur, buckets)
 
 
-def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """fp32 [T, C] in ``groups`` equal parts, each divided by its own root mean square, times weight (csrc/kernels/residual_f32.cu)"""
+def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype, gate: Optional[torch.Tensor] = None,
+                    out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 [T, C] in ``groups`` equal parts, each divided by its own root mean square, times weight; with ``gate`` [T, C] (a column view is
+    fine) also times ``sigmoid(gate)``, then times ``out_scale`` (csrc/kernels/residual_f32.cu).  ``out``: a [T, C] view with unit column
+    stride to write into (e.g. columns of a wider buffer)."""
     if _use_native(x) and x.dtype == torch.float32 and x.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32) and weight.dtype == out_dtype \
-            and x.shape[1] % groups == 0:
-        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        torch.ops.sglb.grouped_rmsnorm(x, weight, int(groups), float(eps), out)
+            and x.shape[1] % groups == 0 and (gate is None or (gate.dtype == out_dtype and gate.stride(1) == 1)):
+        if out is None:
+            out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        assert out.dtype == out_dtype and out.stride(1) == 1
+        torch.ops.sglb.grouped_rmsnorm(x, weight, int(groups), float(eps), out, gate, float(out_scale))
         return out
-    return torch_ref.grouped_rmsnorm(x, weight, groups, eps, out_dtype)
+    y = torch_ref.grouped_rmsnorm(x, weight, groups, eps, out_dtype, gate, out_scale)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
-def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: Optional[torch.Tensor],
-                state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor],
-                H: int, P: int, N: int, G: int) -> torch.Tensor:
+def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
+                A_log: Optional[torch.Tensor], D: Optional[torch.Tensor], state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
+                cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], H: int, P: int, N: int, G: int,
+                decay: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Mamba-2 recurrence over a ragged batch (prompt portions and single decode tokens alike): softplus step size, decay, the fp32 state update
     and read-out, the skip term and the silu(z) gate in one kernel (csrc/kernels/mamba.cu; semantics in ``torch_ref.mamba2_scan``).  ``z`` and
-    ``dt_raw`` may be column views of the projection's output."""
+    ``dt_raw`` may be column views of the projection's output.  ``decay`` fp32 [H] replaces the input-dependent step: step size 1, the
+    head's state times its constant every token (``dt_raw``, ``dt_bias``, ``A_log`` unused)."""
     if (_use_native(u) and u.dtype == torch.float32 and u.is_contiguous() and state.dtype == torch.float32 and N <= 1024 and req_slots.numel() <= 65535
-            and dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32) and (z is None or (z.stride(1) == 1 and z.dtype == dt_raw.dtype))):
+            and (decay is not None or (dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32)))
+            and (z is None or (z.stride(1) == 1 and z.dtype in (torch.bfloat16, torch.float32) and (decay is not None or z.dtype == dt_raw.dtype)))):
         out = torch.empty(u.shape[0], H * P, dtype=torch.float32, device=u.device)
         f = lambda t: None if t is None else t.float().contiguous()
-        torch.ops.sglb.mamba2_scan(u, z, dt_raw, f(dt_bias), f(A_log), f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out)
+        if decay is not None:
+            torch.ops.sglb.mamba2_scan(u, z, None, None, None, f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, f(decay))
+        else:
+            torch.ops.sglb.mamba2_scan(u, z, dt_raw, f(dt_bias), f(A_log), f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, None)
         return out
-    return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G)
+    return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G, decay)
 
 
 def attention_sink_gate(o: torch.Tensor, lse: torch.Tensor, sinks: torch.Tensor, Dv: Optional[int] = None) -> torch.Tensor:
@@ -578,6 +593,27 @@ def attention_sink_gate(o: torch.Tensor, lse: torch.Tensor, sinks: torch.Tensor,
         torch.ops.sglb.attention_sink_gate(o, lse, sinks.float().contiguous(), int(Dv), out)
         return out
     return (o[:, :, :Dv].float() * torch.sigmoid(lse - sinks[None, :]).unsqueeze(-1)).to(o.dtype)
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, Dv: Optional[int] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``o[:, :, :Dv] * sigmoid(gate) * out_scale`` -> [T, H * Dv]: the output gate of an attention whose kernel has no gate epilogue, one number
+    per head (``gate`` [T, H]) or per element ([T, H*Dv]; a column view is fine); also drops zero padding behind ``Dv``
+    (csrc/kernels/window_attention.cu).  ``out``: a [T, H*Dv] view with unit column stride to write into."""
+    T, H = o.shape[0], o.shape[1]
+    Dv = o.shape[2] if Dv is None else Dv
+    if _use_native(o) and o.dtype in (torch.bfloat16, torch.float32) and o.is_contiguous() and gate.dtype == o.dtype and gate.stride(1) == 1 \
+            and gate.shape[1] in (H, H * Dv):
+        if out is None:
+            out = torch.empty(T, H * Dv, dtype=o.dtype, device=o.device)
+        assert out.dtype == o.dtype and out.stride(1) == 1
+        torch.ops.sglb.sigmoid_gate(o, gate, int(Dv), float(out_scale), out)
+        return out
+    g = torch.sigmoid(gate.float())
+    y = (o[:, :, :Dv].float() * (g[:, :, None] if g.shape[1] == H else g.view(T, H, Dv)) * out_scale).to(o.dtype).reshape(T, H * Dv)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
@@ -597,18 +633,82 @@ def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, posi
 def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
                      seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float,
                      softcap: float = 0.0, window: int = -1, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                     dim: int = 0, pad: int = 0) -> torch.Tensor:
+                     dim: int = 0, pad: int = 0, keep_first: int = 0, log_rates: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """paged grouped-query attention with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks, for prompt portions
     and decode tokens (csrc/kernels/window_attention.cu; semantics in ``torch_ref.window_attention``).  Returns [T, H, Dv] in q's dtype.
-    ``pad > 0``: heads are laid out ``pad`` columns wide in q and in the cache rows; ``dim`` is the key size that counts."""
+    ``pad > 0``: heads are laid out ``pad`` columns wide in q and in the cache rows; ``dim`` is the key size that counts.
+    ``keep_first``: the sequence's first positions stay visible behind the window.  ``log_rates``: the bias is ``slopes_h ln(1 + log_rates_h
+    (i - j))``.  ``gate`` [T, H] or [T, H*Dv] (q's dtype, a column view is fine): the output times ``sigmoid(gate)``, per head or per element,
+    then times ``out_scale``, in the kernel's epilogue.  ``out``: a [T, H*Dv] view with unit column stride to write into."""
     T, H, D = q.shape
     if pad > 0:
         D = dim
     if (_use_native(q) and q.dtype in (torch.bfloat16, torch.float32) and q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
-            and D <= 256 and Dv <= 256 and req_slots.numel() <= 65535 and k_cache.stride(0) == v_cache.stride(0)):
-        out = torch.empty(T, H, Dv, dtype=q.dtype, device=q.device)
+            and D <= 256 and Dv <= 256 and req_slots.numel() <= 65535 and k_cache.stride(0) == v_cache.stride(0)
+            and (gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] in (H, H * Dv)))):
+        if out is None:
+            out = torch.empty(T, H * Dv, dtype=q.dtype, device=q.device)
+        assert out.dtype == q.dtype and out.stride(1) == 1 and out.shape == (T, H * Dv)
+        f = lambda t: None if t is None else t.float().contiguous()
         torch.ops.sglb.window_attention(q, k_cache, v_cache, int(G), int(Dv), page_table, req_slots, seq_lens, cu_q, int(max_q_len), int(page_size),
-                                        float(scale), float(softcap), int(window), slopes, sinks, out, int(D), int(pad))
+                                        float(scale), float(softcap), int(window), f(slopes), f(sinks), out, int(D), int(pad), int(keep_first),
+                                        f(log_rates), gate, float(out_scale))
+        return out.view(T, H, Dv) if out.is_contiguous() else out
+    y = torch_ref.window_attention(q, k_cache, v_cache, G, Dv, page_table, req_slots, seq_lens, q_lens, page_size, scale, softcap, window, slopes,
+                                   sinks, dim, pad, keep_first, log_rates, gate, out_scale).to(q.dtype)
+    if out is not None:
+        out.copy_(y.view(T, H * Dv))
         return out
-    return torch_ref.window_attention(q, k_cache, v_cache, G, Dv, page_table, req_slots, seq_lens, q_lens, page_size, scale, softcap, window, slopes,
-                                      sinks, dim, pad).to(q.dtype)
+    return y
+
+
+# ------------------------------------------------------------------ attention preparation / selective scan / element-wise activations
+def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      out_cache_loc: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0) -> torch.Tensor:
+    """what lies between the q / k / v projection and the attention kernel, in one pass per token: an RMS norm of q and of k over their whole
+    projection with a weight, a rotation of the first coordinates of every head by position (pairs half a rotary width apart, angles in
+    fp32 from ``inv_freq``), a blend of v with another layer's values of the same token, and the write of k / v rows into the paged cache
+    (csrc/kernels/window_attention.cu; semantics in ``torch_ref.attention_prepare``).  ``qkv`` may be the first columns of a wider
+    projection; ``v_first`` may be a column view.  Returns q [T, H, D | pad] in the cache dtype."""
+    if (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32) and qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+            and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 and k_cache.stride(0) == v_cache.stride(0)
+            and (v_first is None or (v_first.dtype == qkv.dtype and v_first.stride(1) == 1))
+            and (q_norm_w is None or (q_norm_w.dtype == qkv.dtype and k_norm_w.dtype == qkv.dtype))):
+        q = torch.empty(qkv.shape[0], H, pad if pad > 0 else D, dtype=qkv.dtype, device=qkv.device)
+        torch.ops.sglb.attention_prepare(qkv, int(H), int(G), int(D), int(Dv), positions, k_cache, v_cache, out_cache_loc, q_norm_w, k_norm_w, float(eps),
+                                         inv_freq, v_first, float(v_lambda), q, int(pad))
+        return q
+    return torch_ref.attention_prepare(qkv, H, G, D, Dv, positions, k_cache, v_cache, out_cache_loc, q_norm_w, k_norm_w, eps, inv_freq, v_first, v_lambda, pad)
+
+
+def mamba1_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                D: Optional[torch.Tensor], z: Optional[torch.Tensor], state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
+                cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """selective scan (Mamba-1) over a ragged batch (prompt portions and single decode tokens alike): softplus step size, per-channel and
+    per-state decay ``exp(-dt exp(A_log))``, the fp32 state update and read-out, the skip term and the silu(z) gate in one kernel
+    (csrc/kernels/mamba.cu; semantics in ``torch_ref.mamba1_scan``).  ``dt_raw`` fp32 [T, C]; ``Bm`` / ``Cm`` / ``z`` may be column views of
+    their projections' outputs (bf16 or fp32)."""
+    ok = lambda t: t.stride(1) == 1 and t.dtype in (torch.bfloat16, torch.float32)
+    if (_use_native(u) and u.dtype == torch.float32 and u.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous() and A_log.shape[1] <= 256
+            and req_slots.numel() <= 65535 and dt_raw.dtype == torch.float32 and dt_raw.stride(1) == 1 and ok(Bm) and ok(Cm) and Bm.dtype == Cm.dtype
+            and Bm.stride(0) == Cm.stride(0) and (z is None or ok(z)) and out_dtype in (torch.bfloat16, torch.float32)):
+        out = torch.empty(u.shape, dtype=out_dtype, device=u.device)
+        f = lambda t: None if t is None else t.float().contiguous()
+        torch.ops.sglb.mamba1_scan(u, dt_raw, f(dt_bias), f(A_log), Bm, Cm, f(D), z, state, req_slots, seq_lens, cu_q, out)
+        return out
+    return torch_ref.mamba1_scan(u, dt_raw, dt_bias, A_log, Bm, Cm, D, z, state, req_slots, seq_lens, q_lens, out_dtype)
+
+
+def activation(x: torch.Tensor, kind: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """element-wise ``silu`` or ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) of a [T, n] tensor or column view, fp32 math,
+    into a contiguous tensor of ``out_dtype`` (csrc/kernels/elementwise.cu)"""
+    out_dtype = out_dtype or x.dtype
+    if _use_native(x) and x.dim() == 2 and x.stride(1) == 1 and x.dtype in (torch.bfloat16, torch.float32) and out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        torch.ops.sglb.activation(x, {"silu": 0, "gelu_tanh": 2}[kind], out)
+        return out
+    xf = x.float()
+    y = torch.nn.functional.silu(xf) if kind == "silu" else torch.nn.functional.gelu(xf, approximate="tanh")
+    return y.to(out_dtype)

@@ -95,17 +95,17 @@ def softmax_bias_route(logits: torch.Tensor, correction, top_k: int, n_real: int
 
 def moe_identity_shared_combine(y: torch.Tensor, h: torch.Tensor, ident_w, shared, shared_logit) -> torch.Tensor:
     """y + ident_w * h + sigmoid(shared_logit) * shared, rows of [T, width] (identity experts return their input; the always-on expert is gated
-    by one number per token); fp32 sums (csrc/kernels/moe.cu)"""
+    by one number per token, or joins ungated when ``shared_logit`` is None); fp32 sums (csrc/kernels/moe.cu)"""
     if ident_w is None and shared is None:
         return y
     if y.is_cuda and _has("moe_identity_shared_combine") and y.dtype in (torch.bfloat16, torch.float32) and y.is_contiguous() and h.is_contiguous() \
             and h.dtype == y.dtype and (shared is None or (shared.is_contiguous() and shared.dtype == y.dtype)):
         torch.ops.sglb.moe_identity_shared_combine(y, h, None if ident_w is None else ident_w.float().contiguous(), shared,
-                                                   None if shared is None else shared_logit.float().contiguous())
+                                                   None if shared is None or shared_logit is None else shared_logit.float().contiguous())
         return y
     out = y.float()
     if ident_w is not None:
         out = out + ident_w.float()[:, None] * h.float()
     if shared is not None:
-        out = out + torch.sigmoid(shared_logit.float()).reshape(-1, 1) * shared.float()
+        out = out + (torch.sigmoid(shared_logit.float()).reshape(-1, 1) * shared.float() if shared_logit is not None else shared.float())
     return out.to(y.dtype)

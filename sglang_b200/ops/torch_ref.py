@@ -385,7 +385,7 @@ def add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], weigh
     if delta is not None:
         residual.add_(delta.float())
     y = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
-    w = weight.float()
+    w = weight.float().reshape(-1)          # one element: one gain for all coordinates
     return (y * (1.0 + w if zero_centred else w)).to(out_dtype)
 
 
@@ -508,26 +508,33 @@ def bigram_embedding(embed: torch.Tensor, bigram: Optional[torch.Tensor], ids: t
 
 
 def postnorm_add_rmsnorm_f32(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: torch.Tensor, weight: torch.Tensor, eps: float,
-                             out_dtype: torch.dtype) -> torch.Tensor:
-    """residual (fp32, in place) += rmsnorm(delta) * (1 + post_weight); returns rmsnorm(residual) * (1 + weight) in ``out_dtype``"""
+                             out_dtype: torch.dtype, zero_centred: bool = True) -> torch.Tensor:
+    """residual (fp32, in place) += rmsnorm(delta) * g(post_weight); returns rmsnorm(residual) * g(weight) in ``out_dtype``, with
+    ``g(w) = 1 + w`` (``zero_centred``) or ``w``; a weight of one element is one gain for all coordinates"""
+    g = (lambda w: 1.0 + w.float().reshape(-1)) if zero_centred else (lambda w: w.float().reshape(-1))
     d = delta.float()
-    residual.add_(d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + post_weight.float()))
+    residual.add_(d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * g(post_weight))
     y = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
-    return (y * (1.0 + weight.float())).to(out_dtype)
+    return (y * g(weight)).to(out_dtype)
 
 
-def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """x [T, C] cut into ``groups`` equal parts, each divided by its own root mean square, times weight [C]"""
+def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype, gate: Optional[torch.Tensor] = None,
+                    out_scale: float = 1.0) -> torch.Tensor:
+    """x [T, C] cut into ``groups`` equal parts, each divided by its own root mean square, times weight [C]; with ``gate`` [T, C] also times
+    ``sigmoid(gate)``; times ``out_scale``"""
     T, C = x.shape
     xf = x.float().view(T, groups, C // groups)
-    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
-    return (y.view(T, C) * weight.float()).to(out_dtype)
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).view(T, C) * weight.float()
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float())
+    return (y * out_scale if out_scale != 1.0 else y).to(out_dtype)
 
 
 def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: Optional[torch.Tensor],
                 state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], H: int, P: int, N: int,
-                G: int) -> torch.Tensor:
-    """Mamba-2 recurrence over a ragged batch, token by token, state in place.
+                G: int, decay: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Mamba-2 recurrence over a ragged batch, token by token, state in place.  ``decay`` fp32 [H] (then ``dt_raw``, ``dt_bias`` and ``A_log``
+    are not read): the step size is 1 and every head's state shrinks by its constant, S <- decay_h S + B x^T (linear attention with decay).
 
     u fp32 [T, H*P + 2*G*N] = short-conv outputs [x | B | C]; head h reads B / C group ``h // (H // G)``.  dt = softplus(dt_raw + dt_bias) [T, H]
     (no clamp).  state fp32 [slots, H, N, P]; a request whose ``seq_len == q_len`` starts from zero.  Per token and head:
@@ -538,8 +545,12 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
     x = u[:, :inner].float().view(T, H, P)
     Bm = u[:, inner:inner + G * N].float().view(T, G, N).repeat_interleave(rep, 1)
     Cm = u[:, inner + G * N:inner + 2 * G * N].float().view(T, G, N).repeat_interleave(rep, 1)
-    dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=1e9)
-    dA = torch.exp(-A_log.float().exp()[None, :] * dt)
+    if decay is not None:
+        dt = torch.ones(T, H, dtype=torch.float32, device=u.device)
+        dA = decay.float()[None, :].expand(T, H)
+    else:
+        dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=1e9)
+        dA = torch.exp(-A_log.float().exp()[None, :] * dt)
     out = torch.empty(T, H, P, dtype=torch.float32, device=u.device)
     off = 0
     for b in range(req_slots.shape[0]):
@@ -590,9 +601,13 @@ def qk_norm_cache_write(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, posi
 
 def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, G: int, Dv: int, page_table: torch.Tensor, req_slots: torch.Tensor,
                      seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], page_size: int, scale: float, softcap: float, window: int,
-                     slopes: Optional[torch.Tensor], sinks: Optional[torch.Tensor], dim: int = 0, pad: int = 0) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor], sinks: Optional[torch.Tensor], dim: int = 0, pad: int = 0, keep_first: int = 0,
+                     log_rates: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
     """grouped-query attention over a paged cache with a tanh score cap, a per-head distance bias, a sliding window and soft-max sinks.
     ``pad > 0``: q is [T, H, pad] and every key / value head occupies ``pad`` cache columns, of which the first ``dim`` / ``Dv`` count.
+    ``keep_first``: with a window, the sequence's first ``keep_first`` positions stay visible to every later query.  ``log_rates`` fp32 [H]:
+    the distance bias is ``slopes_h * ln(1 + log_rates_h * (i - j))`` instead of linear.  ``gate`` [T, H] or [T, H*Dv]: the output is
+    multiplied by ``sigmoid(gate)`` per head or per element; ``out_scale`` multiplies it once more.
 
     q [T, H, D]; caches [slots, 1, width] with the G key heads in the first ``G*D`` columns (values: ``G*Dv``); query head h reads key head
     ``h // (H // G)``.  score_ij = cap(q_i . k_j * scale) - slopes_h * (i - j) with cap(s) = softcap * tanh(s / softcap) (``softcap <= 0``:
@@ -613,6 +628,8 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
             continue
         lo = 0 if window <= 0 else max(0, L - ql - window + 1)
         pos = torch.arange(lo, L, device=q.device)
+        if keep_first > 0 and lo > 0:
+            pos = torch.cat([torch.arange(0, min(keep_first, lo), device=q.device), pos])
         slots = page_table[int(req_slots[b]), (pos // page_size).long()].long() * page_size + pos % page_size
         K = k_cache[slots, 0, :G * hk].float().view(-1, G, hk)[:, :, :D].repeat_interleave(rep, 1)
         V = v_cache[slots, 0, :G * hv].float().view(-1, G, hv)[:, :, :Dv].repeat_interleave(rep, 1)
@@ -621,18 +638,24 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
             s = softcap * torch.tanh(s / softcap)
         qpos = torch.arange(L - ql, L, device=q.device)[:, None]
         dist = (qpos - pos[None, :]).float()
-        if slopes is not None:
+        if slopes is not None and log_rates is not None:
+            s = s - slopes.float()[:, None, None] * torch.log(1.0 + log_rates.float()[:, None, None] * dist.clamp(min=0.0)[None])
+        elif slopes is not None:
             s = s - slopes.float()[:, None, None] * dist[None]
         hide = dist < 0
         if window > 0:
-            hide = hide | (dist >= window)
+            far = dist >= window
+            hide = hide | (far & (pos[None, :] >= keep_first) if keep_first > 0 else far)
         s = s.masked_fill(hide[None], float("-inf"))
         if sinks is not None:
             s = torch.cat([s, sinks.float()[:, None, None].expand(H, ql, 1)], -1)
         p = torch.softmax(s, dim=-1)[..., : pos.numel()]
         out[qs:qs + ql] = torch.einsum("hqk,khd->qhd", p, V)
         qs += ql
-    return out
+    if gate is not None:
+        g = torch.sigmoid(gate.float())
+        out = out * (g[:, :, None] if g.shape[1] == H else g.view(T, H, Dv))
+    return out * out_scale if out_scale != 1.0 else out
 
 
 def softmax_bias_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top_k: int, n_real: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -645,3 +668,81 @@ def softmax_bias_route(logits: torch.Tensor, correction: Optional[torch.Tensor],
     w = s.gather(1, ids)
     ident = ids >= n_real
     return w.masked_fill(ident, 0.0).contiguous(), ids.to(torch.int32).contiguous(), (w * ident).sum(-1)
+
+
+# ------------------------------------------------------------------ Resatar mechanisms: attention preparation (projection-wide norm, partial rotation, value mixing), selective scan
+def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      out_cache_loc: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0) -> torch.Tensor:
+    """rows of ``qkv`` [T, >= H*D + G*D + G*Dv] = [q | k | v | ...] -> q [T, H, D] in the cache dtype; k rows to ``k_cache[loc]`` (first
+    ``G*D`` columns), v rows to ``v_cache[loc]`` (first ``G*Dv`` columns).  In this order:
+
+    * ``q_norm_w`` [H*D] / ``k_norm_w`` [G*D]: q and k are RMS-normed over their WHOLE projection (all heads at once), times the weight;
+    * ``inv_freq`` fp32 [R/2]: the first R coordinates of every q and k head are rotated by the angle ``position * inv_freq[i]``, coordinate
+      ``i`` paired with ``i + R/2``;
+    * ``v_first`` [T, G*Dv]: v <- (1 - v_lambda) v + v_lambda v_first before it is cached.
+
+    ``pad > 0``: every head of q, k and v occupies ``pad`` columns, zeros behind its values (q is [T, H, pad])."""
+    T = qkv.shape[0]
+    q = qkv[:, :H * D].float()
+    k = qkv[:, H * D:H * D + G * D].float()
+    v = qkv[:, H * D + G * D:H * D + G * D + G * Dv].float()
+    if q_norm_w is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+    q, k = q.reshape(T, H, D), k.reshape(T, G, D)
+    if inv_freq is not None:
+        half = inv_freq.numel()
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+        def rot(x):
+            a, b = x[..., :half], x[..., half:2 * half]
+            return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * half:]], -1)
+
+        q, k = rot(q), rot(k)
+    if v_first is not None:
+        v = (1.0 - v_lambda) * v + v_lambda * v_first.float()
+    loc = out_cache_loc.long()
+    if pad > 0:
+        zp = lambda t, n: torch.nn.functional.pad(t, (0, pad - n))
+        k_cache[loc, 0, :G * pad] = zp(k, D).reshape(T, G * pad).to(k_cache.dtype)
+        v_cache[loc, 0, :G * pad] = zp(v.reshape(T, G, Dv), Dv).reshape(T, G * pad).to(v_cache.dtype)
+        return zp(q, D).to(k_cache.dtype)
+    k_cache[loc, 0, :G * D] = k.reshape(T, G * D).to(k_cache.dtype)
+    v_cache[loc, 0, :G * Dv] = v.to(v_cache.dtype)
+    return q.to(k_cache.dtype)
+
+
+def mamba1_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                D: Optional[torch.Tensor], z: Optional[torch.Tensor], state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
+                q_lens: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """selective scan (Mamba-1) over a ragged batch, token by token, state in place.
+
+    u fp32 [T, C] short-conv outputs; dt = softplus(dt_raw + dt_bias) [T, C] (no clamp); Bm / Cm [T, N]; state fp32 [slots, 1, C, N]; a request
+    whose ``seq_len == q_len`` starts from zero.  Per token, channel c and state n:  S[c, n] <- exp(-dt_c exp(A_log[c, n])) S[c, n] + dt_c u_c B_n;
+    y_c = sum_n S[c, n] C_n + D_c u_c;  with ``z``: y <- y * silu(z).  Returns [T, C] in ``out_dtype``."""
+    T, C = u.shape
+    x = u.float()
+    dt = dt_raw.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    dt = F.softplus(dt, threshold=1e9)
+    A = -torch.exp(A_log.float())
+    Bf, Cf = Bm.float(), Cm.float()
+    out = torch.empty(T, C, dtype=torch.float32, device=u.device)
+    off = 0
+    for b in range(req_slots.shape[0]):
+        n = 1 if q_lens is None else int(q_lens[b])
+        if n <= 0:
+            continue
+        slot = int(req_slots[b])
+        S = torch.zeros_like(state[slot, 0]) if int(seq_lens[b]) - n == 0 else state[slot, 0].clone()
+        for t in range(off, off + n):
+            S = torch.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * Bf[t][None, :]
+            out[t] = S @ Cf[t]
+        state[slot, 0] = S
+        off += n
+    if D is not None:
+        out = out + D.float()[None, :] * x
+    if z is not None:
+        out = out * F.silu(z.float())
+    return out.to(out_dtype)
