@@ -227,7 +227,7 @@ void add_rmsnorm_f32(at::Tensor residual, c10::optional<at::Tensor> delta, const
   CHECK_CUDA(residual);
   TORCH_CHECK(residual.scalar_type() == at::kFloat && residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && w.is_contiguous());
   TORCH_CHECK(out.scalar_type() == w.scalar_type() && (out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16));
-  TORCH_CHECK(out.numel() == residual.numel() && w.numel() == residual.size(1));
+  TORCH_CHECK(out.numel() == residual.numel() && (w.numel() == residual.size(1) || w.numel() == 1));          // one element: one gain for all
   bool dbf = false;
   if (delta.has_value()) {
     TORCH_CHECK(delta->is_contiguous() && delta->numel() == residual.numel() && (delta->scalar_type() == at::kFloat || delta->scalar_type() == at::kBFloat16));
@@ -235,7 +235,8 @@ void add_rmsnorm_f32(at::Tensor residual, c10::optional<at::Tensor> delta, const
   }
   c10::cuda::CUDAGuard g(residual.device());
   sglb::add_rmsnorm_f32(residual.data_ptr<float>(), delta.has_value() ? delta->data_ptr() : nullptr, dbf, w.data_ptr(), out.data_ptr(),
-                        out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, zero_centred, cur_stream());
+                        out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, zero_centred,
+                        w.numel() == 1 && residual.size(1) != 1 ? 0 : 1, cur_stream());
   count();
 }
 
@@ -299,47 +300,65 @@ void bigram_embedding(const at::Tensor& embed, c10::optional<at::Tensor> bigram,
   count();
 }
 
-void postnorm_add_rmsnorm_f32(at::Tensor residual, const at::Tensor& delta, const at::Tensor& post_w, const at::Tensor& w, at::Tensor out, double eps) {
+void postnorm_add_rmsnorm_f32(at::Tensor residual, const at::Tensor& delta, const at::Tensor& post_w, const at::Tensor& w, at::Tensor out, double eps,
+                              bool zero_centred) {
   CHECK_CUDA(residual);
   TORCH_CHECK(residual.scalar_type() == at::kFloat && residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && w.is_contiguous() &&
               post_w.is_contiguous() && delta.is_contiguous() && bf16_or_f32(out) && bf16_or_f32(delta));
   TORCH_CHECK(out.scalar_type() == w.scalar_type() && out.scalar_type() == post_w.scalar_type() && out.numel() == residual.numel() &&
-              delta.numel() == residual.numel() && w.numel() == residual.size(1) && post_w.numel() == residual.size(1));
+              delta.numel() == residual.numel() && (w.numel() == residual.size(1) || w.numel() == 1) &&
+              (post_w.numel() == residual.size(1) || post_w.numel() == 1));
   c10::cuda::CUDAGuard g(residual.device());
   sglb::postnorm_add_rmsnorm_f32(residual.data_ptr<float>(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, post_w.data_ptr(), w.data_ptr(),
-                                 out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, cur_stream());
+                                 out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)residual.size(0), (int)residual.size(1), (float)eps, zero_centred,
+                                 post_w.numel() == 1 && residual.size(1) != 1 ? 0 : 1, w.numel() == 1 && residual.size(1) != 1 ? 0 : 1, cur_stream());
   count();
 }
 
-void grouped_rmsnorm(const at::Tensor& x, const at::Tensor& w, int64_t groups, double eps, at::Tensor out) {
+void grouped_rmsnorm(const at::Tensor& x, const at::Tensor& w, int64_t groups, double eps, at::Tensor out, c10::optional<at::Tensor> gate, double out_scale) {
   CHECK_CUDA(x);
-  TORCH_CHECK(x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous() && out.is_contiguous() && w.is_contiguous() && bf16_or_f32(out) &&
-              out.scalar_type() == w.scalar_type() && out.numel() == x.numel() && w.numel() == x.size(1));
+  TORCH_CHECK(x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous() && out.dim() == 2 && out.stride(1) == 1 && w.is_contiguous() &&
+              bf16_or_f32(out) && out.scalar_type() == w.scalar_type() && out.size(0) == x.size(0) && out.size(1) == x.size(1) && w.numel() == x.size(1));
+  if (gate.has_value())
+    TORCH_CHECK(gate->scalar_type() == out.scalar_type() && gate->dim() == 2 && gate->stride(1) == 1 && gate->size(0) == x.size(0) &&
+                gate->size(1) == x.size(1));
+  if (x.size(0) == 0) return;
   c10::cuda::CUDAGuard g(x.device());
   sglb::grouped_rmsnorm(x.data_ptr<float>(), w.data_ptr(), out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)x.size(0), (int)x.size(1), (int)groups,
-                        (float)eps, cur_stream());
+                        (float)eps, gate.has_value() ? gate->data_ptr() : nullptr, gate.has_value() ? (int)gate->stride(0) : 0, (int)out.stride(0),
+                        (float)out_scale, cur_stream());
   count();
 }
 
-void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, const at::Tensor& dt_raw, const at::Tensor& dt_bias, const at::Tensor& A_log,
-                 c10::optional<at::Tensor> D, at::Tensor state, const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q,
-                 int64_t H, int64_t P, int64_t N, int64_t G, at::Tensor out) {
+void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, c10::optional<at::Tensor> dt_raw, c10::optional<at::Tensor> dt_bias,
+                 c10::optional<at::Tensor> A_log, c10::optional<at::Tensor> D, at::Tensor state, const at::Tensor& req_slots, const at::Tensor& seq_lens,
+                 c10::optional<at::Tensor> cu_q, int64_t H, int64_t P, int64_t N, int64_t G, at::Tensor out, c10::optional<at::Tensor> decay) {
   CHECK_CUDA(u); CHECK_I32(req_slots); CHECK_I32(seq_lens);
   auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
-  TORCH_CHECK(f32c(u) && f32c(dt_bias) && f32c(A_log) && f32c(state) && f32c(out) && u.dim() == 2 && u.size(1) >= H * P + 2 * G * N);
-  TORCH_CHECK(bf16_or_f32(dt_raw) && dt_raw.dim() == 2 && dt_raw.stride(1) == 1 && dt_raw.size(1) >= H && dt_raw.size(0) == u.size(0));
-  if (z.has_value()) TORCH_CHECK(z->scalar_type() == dt_raw.scalar_type() && z->dim() == 2 && z->stride(1) == 1 && z->size(1) >= H * P && z->size(0) == u.size(0));
+  TORCH_CHECK(f32c(u) && f32c(state) && f32c(out) && u.dim() == 2 && u.size(1) >= H * P + 2 * G * N);
+  bool in_bf16 = false;
+  if (decay.has_value()) {          // constant decay per head, step size 1: no step-size inputs
+    TORCH_CHECK(f32c(*decay) && decay->numel() == H);
+    if (z.has_value()) in_bf16 = z->scalar_type() == at::kBFloat16;
+  } else {
+    TORCH_CHECK(dt_raw.has_value() && dt_bias.has_value() && A_log.has_value() && f32c(*dt_bias) && f32c(*A_log) && dt_bias->numel() == H && A_log->numel() == H);
+    TORCH_CHECK(bf16_or_f32(*dt_raw) && dt_raw->dim() == 2 && dt_raw->stride(1) == 1 && dt_raw->size(1) >= H && dt_raw->size(0) == u.size(0));
+    in_bf16 = dt_raw->scalar_type() == at::kBFloat16;
+    if (z.has_value()) TORCH_CHECK(z->scalar_type() == dt_raw->scalar_type());
+  }
+  if (z.has_value()) TORCH_CHECK(bf16_or_f32(*z) && z->dim() == 2 && z->stride(1) == 1 && z->size(1) >= H * P && z->size(0) == u.size(0));
   if (D.has_value()) TORCH_CHECK(f32c(*D) && D->numel() == H);
-  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == N && state.size(3) == P && dt_bias.numel() == H && A_log.numel() == H &&
-              out.size(0) == u.size(0) && out.numel() == u.size(0) * H * P);
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == N && state.size(3) == P && out.size(0) == u.size(0) &&
+              out.numel() == u.size(0) * H * P);
   const int B = (int)req_slots.size(0);
   if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(u.size(0) == B);
   if (u.size(0) == 0) return;
   c10::cuda::CUDAGuard g(u.device());
   sglb::mamba2_scan(u.data_ptr<float>(), (int)u.stride(0), z.has_value() ? z->data_ptr() : nullptr, z.has_value() ? (int)z->stride(0) : 0,
-                    dt_raw.data_ptr(), (int)dt_raw.stride(0), dt_raw.scalar_type() == at::kBFloat16, dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
-                    opt_ptr<float>(D), state.data_ptr<float>(), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, (int)H, (int)P,
-                    (int)N, (int)G, out.data_ptr<float>(), cur_stream());
+                    decay.has_value() ? nullptr : dt_raw->data_ptr(), decay.has_value() ? 0 : (int)dt_raw->stride(0), in_bf16,
+                    decay.has_value() ? nullptr : dt_bias->data_ptr<float>(), decay.has_value() ? nullptr : A_log->data_ptr<float>(), opt_ptr<float>(D),
+                    state.data_ptr<float>(), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, (int)H, (int)P, (int)N, (int)G,
+                    out.data_ptr<float>(), opt_ptr<float>(decay), cur_stream());
   count();
 }
 
@@ -362,10 +381,12 @@ void qk_norm_cache_write(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D,
 void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, int64_t G, int64_t Dv, const at::Tensor& page_table,
                       const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t page_size,
                       double scale, double softcap, int64_t window, c10::optional<at::Tensor> slopes, c10::optional<at::Tensor> sinks, at::Tensor out,
-                      int64_t dim, int64_t pad) {
+                      int64_t dim, int64_t pad, int64_t keep_first, c10::optional<at::Tensor> log_rates, c10::optional<at::Tensor> gate, double out_scale) {
   CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
-  TORCH_CHECK(bf16_or_f32(q) && q.dim() == 3 && q.is_contiguous() && out.is_contiguous() && out.scalar_type() == q.scalar_type() &&
-              out.numel() == q.size(0) * q.size(1) * Dv);
+  // out: [T, H, Dv] contiguous, or a [T, H * Dv] block of columns of a wider buffer
+  TORCH_CHECK(bf16_or_f32(q) && q.dim() == 3 && q.is_contiguous() && out.scalar_type() == q.scalar_type() && out.numel() == q.size(0) * q.size(1) * Dv &&
+              (out.is_contiguous() || (out.dim() == 2 && out.stride(1) == 1 && out.size(1) == q.size(1) * Dv)));
+  const int ldo = out.dim() == 2 ? (int)out.stride(0) : (int)(q.size(1) * Dv);
   // pad > 0: q [T, H, pad] and every key / value head occupy ``pad`` columns of which the first ``dim`` / ``Dv`` count
   const int64_t H = q.size(1), D = pad > 0 ? dim : q.size(2);
   TORCH_CHECK(pad == 0 || (q.size(2) == pad && D >= 1 && D <= pad && Dv <= pad));
@@ -376,12 +397,105 @@ void window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::
   if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(q.size(0) == B);
   if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->is_contiguous() && sinks->numel() == H);
   if (slopes.has_value()) TORCH_CHECK(slopes->scalar_type() == at::kFloat && slopes->is_contiguous() && slopes->numel() == H);
+  if (log_rates.has_value()) TORCH_CHECK(slopes.has_value() && log_rates->scalar_type() == at::kFloat && log_rates->is_contiguous() && log_rates->numel() == H);
+  bool gate_per_head = false;
+  if (gate.has_value()) {
+    TORCH_CHECK(gate->scalar_type() == q.scalar_type() && gate->dim() == 2 && gate->stride(1) == 1 && gate->size(0) == q.size(0) &&
+                (gate->size(1) == H || gate->size(1) == H * Dv));
+    gate_per_head = gate->size(1) == H && Dv != 1;
+  }
   if (q.size(0) == 0) return;
   c10::cuda::CUDAGuard g(q.device());
   sglb::window_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q.scalar_type() == at::kBFloat16, (size_t)k_cache.stride(0), (int)H, (int)G,
                          (int)D, (int)Dv, page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(),
                          seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, cu_q.has_value() ? (int)max_q_len : 1, (float)scale, (float)softcap, (int)window,
-                         opt_ptr<float>(slopes), opt_ptr<float>(sinks), out.data_ptr(), (int)pad, cur_stream());
+                         opt_ptr<float>(slopes), opt_ptr<float>(sinks), out.data_ptr(), (int)pad, (int)keep_first, opt_ptr<float>(log_rates),
+                         gate.has_value() ? gate->data_ptr() : nullptr, gate.has_value() ? (int)gate->stride(0) : 0, gate_per_head, ldo, (float)out_scale,
+                         cur_stream());
+  count();
+}
+
+void mamba1_scan(const at::Tensor& u, const at::Tensor& dt_raw, c10::optional<at::Tensor> dt_bias, const at::Tensor& A_log, const at::Tensor& Bm,
+                 const at::Tensor& Cm, c10::optional<at::Tensor> D, c10::optional<at::Tensor> z, at::Tensor state, const at::Tensor& req_slots,
+                 const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, at::Tensor out) {
+  CHECK_CUDA(u); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
+  const int64_t T = u.size(0), C = u.size(1), N = A_log.size(1);
+  TORCH_CHECK(f32c(u) && f32c(A_log) && f32c(state) && u.dim() == 2 && A_log.dim() == 2 && A_log.size(0) == C && out.is_contiguous() && bf16_or_f32(out) &&
+              out.numel() == u.numel());
+  TORCH_CHECK(dt_raw.scalar_type() == at::kFloat && dt_raw.dim() == 2 && dt_raw.stride(1) == 1 && dt_raw.size(0) == T && dt_raw.size(1) == C);
+  TORCH_CHECK(bf16_or_f32(Bm) && Bm.scalar_type() == Cm.scalar_type() && Bm.dim() == 2 && Cm.dim() == 2 && Bm.stride(1) == 1 && Cm.stride(1) == 1 &&
+              Bm.stride(0) == Cm.stride(0) && Bm.size(0) == T && Cm.size(0) == T && Bm.size(1) == N && Cm.size(1) == N);
+  if (dt_bias.has_value()) TORCH_CHECK(f32c(*dt_bias) && dt_bias->numel() == C);
+  if (D.has_value()) TORCH_CHECK(f32c(*D) && D->numel() == C);
+  if (z.has_value()) TORCH_CHECK(bf16_or_f32(*z) && z->dim() == 2 && z->stride(1) == 1 && z->size(0) == T && z->size(1) == C);
+  TORCH_CHECK(state.numel() == state.size(0) * C * N);
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(T == B);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(u.device());
+  sglb::mamba1_scan(u.data_ptr<float>(), dt_raw.data_ptr<float>(), (int)dt_raw.stride(0), opt_ptr<float>(dt_bias), A_log.data_ptr<float>(), Bm.data_ptr(),
+                    Cm.data_ptr(), (int)Bm.stride(0), Bm.scalar_type() == at::kBFloat16, opt_ptr<float>(D), z.has_value() ? z->data_ptr() : nullptr,
+                    z.has_value() ? (int)z->stride(0) : 0, z.has_value() && z->scalar_type() == at::kBFloat16, state.data_ptr<float>(),
+                    req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, (int)C, (int)N, out.data_ptr(),
+                    out.scalar_type() == at::kBFloat16, cur_stream());
+  count();
+}
+
+void attention_prepare(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D, int64_t Dv, const at::Tensor& positions, at::Tensor k_cache, at::Tensor v_cache,
+                       const at::Tensor& loc, c10::optional<at::Tensor> q_norm_w, c10::optional<at::Tensor> k_norm_w, double eps,
+                       c10::optional<at::Tensor> inv_freq, c10::optional<at::Tensor> v_first, double v_lambda, at::Tensor q_out, int64_t pad) {
+  CHECK_CUDA(qkv); CHECK_I32(positions); CHECK_I32(loc);
+  const int64_t T = qkv.size(0);
+  TORCH_CHECK(bf16_or_f32(qkv) && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) >= H * D + G * D + G * Dv && H % G == 0);
+  TORCH_CHECK(pad == 0 || (D <= pad && Dv <= pad));
+  const int64_t hs = pad > 0 ? pad : D, hv = pad > 0 ? pad : Dv;
+  TORCH_CHECK(q_out.is_contiguous() && q_out.scalar_type() == qkv.scalar_type() && q_out.numel() == T * H * hs);
+  TORCH_CHECK(k_cache.scalar_type() == qkv.scalar_type() && v_cache.scalar_type() == qkv.scalar_type() && k_cache.dim() == 3 && k_cache.size(1) == 1 &&
+              k_cache.stride(2) == 1 && v_cache.stride(2) == 1 && k_cache.stride(0) == v_cache.stride(0) && k_cache.size(2) >= G * hs &&
+              v_cache.size(2) >= G * hv && positions.numel() == T && loc.numel() == T);
+  TORCH_CHECK(q_norm_w.has_value() == k_norm_w.has_value());
+  if (q_norm_w.has_value())
+    TORCH_CHECK(q_norm_w->scalar_type() == qkv.scalar_type() && k_norm_w->scalar_type() == qkv.scalar_type() && q_norm_w->is_contiguous() &&
+                k_norm_w->is_contiguous() && q_norm_w->numel() == H * D && k_norm_w->numel() == G * D);
+  int half = 0;
+  if (inv_freq.has_value()) {
+    TORCH_CHECK(inv_freq->scalar_type() == at::kFloat && inv_freq->is_contiguous() && 2 * inv_freq->numel() <= D);
+    half = (int)inv_freq->numel();
+  }
+  if (v_first.has_value())
+    TORCH_CHECK(v_first->scalar_type() == qkv.scalar_type() && v_first->dim() == 2 && v_first->stride(1) == 1 && v_first->size(0) == T &&
+                v_first->size(1) == G * Dv);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(qkv.device());
+  sglb::attention_prepare(qkv.data_ptr(), (int)qkv.stride(0), qkv.scalar_type() == at::kBFloat16, (int)T, (int)H, (int)G, (int)D, (int)Dv,
+                          positions.data_ptr<int>(), q_norm_w.has_value() ? q_norm_w->data_ptr() : nullptr, k_norm_w.has_value() ? k_norm_w->data_ptr() : nullptr,
+                          (float)eps, half > 0 ? inv_freq->data_ptr<float>() : nullptr, half, v_first.has_value() ? v_first->data_ptr() : nullptr,
+                          v_first.has_value() ? (int)v_first->stride(0) : 0, (float)v_lambda, k_cache.data_ptr(), v_cache.data_ptr(), (size_t)k_cache.stride(0),
+                          loc.data_ptr<int>(), q_out.data_ptr(), (int)pad, cur_stream());
+  count();
+}
+
+void sigmoid_gate(const at::Tensor& o, const at::Tensor& gate, int64_t Dv, double out_scale, at::Tensor out) {
+  CHECK_CUDA(o);
+  const int64_t T = o.size(0), H = o.size(1);
+  TORCH_CHECK(bf16_or_f32(o) && o.dim() == 3 && o.is_contiguous() && Dv >= 1 && Dv <= o.size(2) && out.scalar_type() == o.scalar_type() && out.dim() == 2 &&
+              out.stride(1) == 1 && out.size(0) == T && out.size(1) == H * Dv);
+  TORCH_CHECK(gate.scalar_type() == o.scalar_type() && gate.dim() == 2 && gate.stride(1) == 1 && gate.size(0) == T && (gate.size(1) == H || gate.size(1) == H * Dv));
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(o.device());
+  sglb::sigmoid_gate(o.data_ptr(), (int)o.size(2), gate.data_ptr(), (int)gate.stride(0), gate.size(1) == H && Dv != 1, o.scalar_type() == at::kBFloat16, (int)T,
+                     (int)H, (int)Dv, (float)out_scale, out.data_ptr(), (int)out.stride(0), cur_stream());
+  count();
+}
+
+void activation(const at::Tensor& x, int64_t act, at::Tensor out) {
+  CHECK_CUDA(x);
+  TORCH_CHECK(bf16_or_f32(x) && bf16_or_f32(out) && x.dim() == 2 && x.stride(1) == 1 && out.is_contiguous() && out.numel() == x.numel() && (act == 0 || act == 2));
+  if (x.numel() == 0) return;
+  c10::cuda::CUDAGuard g(x.device());
+  sglb::activation(x.data_ptr(), (int)x.stride(0), x.scalar_type() == at::kBFloat16, out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)x.size(0),
+                   (int)x.size(1), (int)act, cur_stream());
   count();
 }
 
@@ -416,12 +530,13 @@ void moe_identity_shared_combine(at::Tensor y, const at::Tensor& h, c10::optiona
   TORCH_CHECK(bf16_or_f32(y) && y.dim() == 2 && y.is_contiguous() && h.is_contiguous() && h.scalar_type() == y.scalar_type() && h.numel() == y.numel());
   if (ident.has_value()) TORCH_CHECK(ident->scalar_type() == at::kFloat && ident->is_contiguous() && ident->numel() == y.size(0));
   if (shared.has_value())
-    TORCH_CHECK(shared->scalar_type() == y.scalar_type() && shared->is_contiguous() && shared->numel() == y.numel() && gate.has_value() &&
-                gate->scalar_type() == at::kFloat && gate->is_contiguous() && gate->numel() == y.size(0));
+    TORCH_CHECK(shared->scalar_type() == y.scalar_type() && shared->is_contiguous() && shared->numel() == y.numel() &&
+                (!gate.has_value() || (gate->scalar_type() == at::kFloat && gate->is_contiguous() && gate->numel() == y.size(0))));
   if (y.size(0) == 0 || (!ident.has_value() && !shared.has_value())) return;
   c10::cuda::CUDAGuard g(y.device());
   sglb::moe_identity_shared_combine(y.data_ptr(), h.data_ptr(), opt_ptr<float>(ident), shared.has_value() ? shared->data_ptr() : nullptr,
-                                    shared.has_value() ? gate->data_ptr<float>() : nullptr, y.scalar_type() == at::kBFloat16, (int)y.size(0), (int)y.size(1),
+                                    shared.has_value() && gate.has_value() ? gate->data_ptr<float>() : nullptr, y.scalar_type() == at::kBFloat16, (int)y.size(0),
+                                    (int)y.size(1),
                                     cur_stream());
   count();
 }
@@ -869,14 +984,22 @@ TORCH_LIBRARY(sglb, m) {
   m.def("clamped_glu(Tensor gu, Tensor(a!) out, float limit, float alpha) -> ()", &clamped_glu);
   m.def("bigram_embedding(Tensor embed, Tensor? bigram, Tensor ids, Tensor(a!)? prev_tokens, Tensor? cu_q, Tensor req_slots, Tensor seq_lens, "
         "int max_q_len, float scale, int mul_prev, int mul_cur, int buckets, Tensor(b!) out) -> ()", &bigram_embedding);
-  m.def("postnorm_add_rmsnorm_f32(Tensor(a!) residual, Tensor delta, Tensor post_w, Tensor w, Tensor(b!) out, float eps) -> ()", &postnorm_add_rmsnorm_f32);
-  m.def("grouped_rmsnorm(Tensor x, Tensor w, int groups, float eps, Tensor(a!) out) -> ()", &grouped_rmsnorm);
-  m.def("mamba2_scan(Tensor u, Tensor? z, Tensor dt_raw, Tensor dt_bias, Tensor A_log, Tensor? D, Tensor(a!) state, Tensor req_slots, Tensor seq_lens, "
-        "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out) -> ()", &mamba2_scan);
+  m.def("postnorm_add_rmsnorm_f32(Tensor(a!) residual, Tensor delta, Tensor post_w, Tensor w, Tensor(b!) out, float eps, bool zero_centred=True) -> ()",
+        &postnorm_add_rmsnorm_f32);
+  m.def("grouped_rmsnorm(Tensor x, Tensor w, int groups, float eps, Tensor(a!) out, Tensor? gate=None, float out_scale=1.0) -> ()", &grouped_rmsnorm);
+  m.def("mamba2_scan(Tensor u, Tensor? z, Tensor? dt_raw, Tensor? dt_bias, Tensor? A_log, Tensor? D, Tensor(a!) state, Tensor req_slots, Tensor seq_lens, "
+        "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out, Tensor? decay=None) -> ()", &mamba2_scan);
+  m.def("mamba1_scan(Tensor u, Tensor dt_raw, Tensor? dt_bias, Tensor A_log, Tensor Bm, Tensor Cm, Tensor? D, Tensor? z, Tensor(a!) state, Tensor req_slots, "
+        "Tensor seq_lens, Tensor? cu_q, Tensor(b!) out) -> ()", &mamba1_scan);
+  m.def("attention_prepare(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, Tensor? q_norm_w, "
+        "Tensor? k_norm_w, float eps, Tensor? inv_freq, Tensor? v_first, float v_lambda, Tensor(c!) q_out, int pad=0) -> ()", &attention_prepare);
+  m.def("sigmoid_gate(Tensor o, Tensor gate, int Dv, float out_scale, Tensor(a!) out) -> ()", &sigmoid_gate);
+  m.def("activation(Tensor x, int act, Tensor(a!) out) -> ()", &activation);
   m.def("qk_norm_cache_write(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, float eps, float temp_coef, int temp_every, "
         "Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, bool normalise, Tensor(c!) q_out, int pad=0) -> ()", &qk_norm_cache_write);
   m.def("window_attention(Tensor q, Tensor k_cache, Tensor v_cache, int G, int Dv, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
-        "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out, int dim=0, int pad=0) -> ()",
+        "int max_q_len, int page_size, float scale, float softcap, int window, Tensor? slopes, Tensor? sinks, Tensor(a!) out, int dim, int pad=0, "
+        "int keep_first=0, Tensor? log_rates=None, Tensor? gate=None, float out_scale=1.0) -> ()",
         &window_attention);
   m.def("attention_sink_gate(Tensor o, Tensor lse, Tensor sinks, int Dv, Tensor(a!) out) -> ()", &attention_sink_gate);
   m.def("moe_softmax_bias_route(Tensor logits, Tensor? corr, int n_real, Tensor(a!) w, Tensor(b!) ids, Tensor(c!) ident) -> ()", &moe_softmax_bias_route);

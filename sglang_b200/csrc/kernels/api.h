@@ -102,7 +102,7 @@ bool gated_delta_update(float* state, const int* req_slots, const float* u, int 
                         int Hv, int r, int Dk, int Dv, float* out, cudaStream_t stream);
 // residual_f32.cu
 void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
-                     bool zero_centred, cudaStream_t stream);
+                     bool zero_centred, int w_stride, cudaStream_t stream);
 void clamped_glu(const void* gu, void* out, bool bf16, int T, int I, float limit, float alpha, cudaStream_t stream);
 // delta_rule.cu
 bool gated_delta_rule(const float* u, int ldu, int Hk, int Dk, int H, int Dv, const float* a_raw, bool per_channel, const float* A_log,
@@ -113,15 +113,26 @@ void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G
                          void* kc, void* vc, size_t ldc, const int* loc, bool normalise, void* q_out, int pad, cudaStream_t stream);
 void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
                       int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
-                      float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, cudaStream_t stream);
+                      float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, int keep_first, const float* log_rates,
+                      const void* gate, int ldg, bool gate_per_head, int ldo, float out_scale, cudaStream_t stream);
+void sigmoid_gate(const void* o, int head_stride, const void* gate, int ldg, bool per_head, bool bf16, int T, int H, int Dv, float scale, void* out, int ldo,
+                  cudaStream_t stream);
+void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, const void* q_norm_w, const void* k_norm_w,
+                       float eps, const float* inv_freq, int half, const void* v_first, int ldvf, float lam, void* kc, void* vc, size_t ldc, const int* loc,
+                       void* q_out, int pad, cudaStream_t stream);
 void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream);
 // mamba.cu (ragged Mamba-2 recurrence), residual_f32.cu (sandwich norms), elementwise.cu (bigram embedding), moe.cu (identity / shared experts)
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
                  const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
-                 cudaStream_t stream);
+                 const float* decay, cudaStream_t stream);
+void mamba1_scan(const float* u, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log, const void* Bm, const void* Cm, int ldbc, bool bc_bf16,
+                 const float* D, const void* z, int ldz, bool z_bf16, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int C,
+                 int N, void* out, bool out_bf16, cudaStream_t stream);
+void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, cudaStream_t stream);
 void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
-                              int H, float eps, cudaStream_t stream);
-void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, cudaStream_t stream);
+                              int H, float eps, bool zero_centred, int post_w_stride, int w_stride, cudaStream_t stream);
+void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, const void* gate, int ldg, int ldo,
+                     float out_scale, cudaStream_t stream);
 void bigram_embedding(const void* embed, const void* bigram, bool bf16, const int* ids, int* prev_tokens, const int* cu_q, const int* req_slots,
                       const int* seq_lens, int B, int max_q_len, int W, int vocab, float scale, long long mul_prev, long long mul_cur, int buckets,
                       float* out, cudaStream_t stream);

@@ -455,4 +455,37 @@ void bigram_embedding(const void* embed, const void* bigram, bool bf16, const in
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------- act(x) element-wise, [T, n] rows of ldx elements -> contiguous [T, n]
+template <typename TI, typename TO, int ACT>  // 0 silu, 2 gelu(tanh)
+__global__ void __launch_bounds__(256) activation_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n) {
+  const size_t total = (size_t)T * n;
+  for (size_t idx = blockIdx.x * (size_t)256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const size_t t = idx / n;
+    const int i = (int)(idx - t * n);
+    float v;
+    if constexpr (sizeof(TI) == 2) v = __bfloat162float(x[t * ldx + i]); else v = x[t * ldx + i];
+    float a;
+    if (ACT == 0) a = v / (1.f + expf(-v));
+    else { const float c = 0.7978845608028654f * (v + 0.044715f * v * v * v); a = 0.5f * v * (1.f + tanhf(c)); }
+    if constexpr (sizeof(TO) == 2) out[idx] = __float2bfloat16(a); else out[idx] = a;
+  }
+}
+
+void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return;
+  const size_t total = (size_t)T * n;
+  const size_t gq = (total + 255) / 256;
+  const int grid = (int)(gq < (size_t)(148 * 16) ? gq : (size_t)(148 * 16));
+  using bf = __nv_bfloat16;
+#define SGLB_ACT(TI, TO)                                                                                                   \
+  do {                                                                                                                     \
+    if (act == 0) activation_kernel<TI, TO, 0><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n);               \
+    else activation_kernel<TI, TO, 2><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n);                        \
+  } while (0)
+  if (x_bf16) { if (out_bf16) SGLB_ACT(bf, bf); else SGLB_ACT(bf, float); }
+  else { if (out_bf16) SGLB_ACT(float, bf); else SGLB_ACT(float, float); }
+#undef SGLB_ACT
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 }  // namespace sglb

@@ -257,6 +257,7 @@ struct Mamba2Params {
   const void* z; int ldz;                        // gate rows (model dtype) or null
   const void* dt_raw; int lddt;                  // [T, >= H] (model dtype)
   const float* dt_bias; const float* A_log; const float* D;
+  const float* decay;                            // non-null: step size 1 and the head's constant decay (dt_raw, dt_bias, A_log unused)
   float* state;                                  // [slots, H, N, P]
   const int* req_slots; const int* seq_lens; const int* cu_q;
   float* out;                                    // [T, H*P]
@@ -308,9 +309,10 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
     for (int idx = tid; idx < 2 * stage; idx += 128) sm[idx] = 0.f;
     __syncthreads();
   }
-  const float a_exp = expf(p.A_log[h]);
+  const float a_exp = p.decay ? 0.f : expf(p.A_log[h]);
   const float dskip = p.D ? p.D[h] : 0.f;
-  const float dtb = p.dt_bias[h];
+  const float dtb = p.decay ? 0.f : p.dt_bias[h];
+  const float fixed_decay = p.decay ? p.decay[h] : 0.f;
   const TZ* zg = reinterpret_cast<const TZ*>(p.z);
   const TZ* dg = reinterpret_cast<const TZ*>(p.dt_raw);
   const int inner = H * P;
@@ -337,7 +339,7 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
       const int idx = tid + k * 128, tt = idx / PC, c = idx - tt * PC;
       zr[k] = (zg && tt < tc && c < pw) ? ld_f<TZ>(zg + (size_t)(q0 + t0 + tt) * p.ldz + h * P + pc * PC + c) : 0.f;
     }
-    if (tid < tc) dtr = ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h);
+    if (dg && tid < tc) dtr = ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h);
   };
   auto land = [&](int t0, float* buf) {       // finish what issue() started
     const int tc = min(TC, n - t0);
@@ -348,9 +350,9 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
       if (idx < TC * PC) sZ[idx] = zr[k];
     }
     if (tid < tc) {
-      const float dt = m2_softplus(dtr + dtb);
+      const float dt = p.decay ? 1.f : m2_softplus(dtr + dtb);
       sDt[tid] = dt;
-      sDa[tid] = expf(-a_exp * dt);
+      sDa[tid] = p.decay ? fixed_decay : expf(-a_exp * dt);
     }
     m2_cp_wait();
   };
@@ -464,14 +466,172 @@ void dispatch_m2(const Mamba2Params& p, int B, cudaStream_t stream) {
 
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
                  const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
-                 cudaStream_t stream) {
+                 const float* decay, cudaStream_t stream) {
   if (B <= 0) return;
   if (N > 1024 || B > 65535 || H % G) throw std::runtime_error("sglb mamba2_scan: state size up to 1024, heads a multiple of groups");
+  if (!decay && (!dt_raw || !dt_bias || !A_log)) throw std::runtime_error("sglb mamba2_scan: step-size inputs or a constant decay");
   Mamba2Params p;
+  p.decay = decay;
   p.u = u; p.ldu = ldu; p.z = z; p.ldz = ldz; p.dt_raw = dt_raw; p.lddt = lddt; p.dt_bias = dt_bias; p.A_log = A_log; p.D = D; p.state = state;
   p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.out = out; p.H = H; p.P = P; p.N = N; p.G = G; p.pchunks = 1;
   if (bf16) dispatch_m2<__nv_bfloat16>(p, B, stream);
   else dispatch_m2<float>(p, B, stream);
+}
+
+// ---------------------------------------------------------------- Mamba-1 selective scan over a ragged batch
+//   dt = softplus(dt_raw + dt_bias) per channel;  S[c, n] <- exp(-dt_c exp(A_log[c, n])) S[c, n] + dt_c u_c B_n;  y_c = sum_n S[c, n] C_n + D_c u_c;
+//   y <- y * silu(z).  State fp32 [slots, C, N]; a request whose cached length is zero starts from S = 0 whatever its slot holds.
+// Mapping: CTA = (block of CH channels, request), 128 threads; a channel's N states lie in the registers of LPC neighbouring lanes, NPT per
+// lane (A likewise: exp(A_log) is computed once per call); tokens are staged TC at a time through shared memory (B, C per state; dt, u, z
+// per channel), so the serial chain reads no global memory; the read-out is reduced over the channel's lanes with shuffles and leaves
+// through shared memory in rows.  Token order is fixed: a position's output is bit-identical however the prompt was cut or batched.
+namespace {
+
+struct Mamba1Params {
+  const float* u; const float* dt_raw; int lddt;
+  const float* dt_bias; const float* A_log;
+  const void* Bm; const void* Cm; int ldbc;
+  const float* D; const void* z; int ldz;
+  float* state;
+  const int* req_slots; const int* seq_lens; const int* cu_q;
+  void* out;
+  int C, N;
+};
+
+template <typename T> __device__ __forceinline__ float m1_ld(const T* p);
+template <> __device__ __forceinline__ float m1_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float m1_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void m1_st(T* p, float v);
+template <> __device__ __forceinline__ void m1_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void m1_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename TBC, typename TZ, typename TO, int NPT, int LPC, int TC>
+__global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) {
+  constexpr int CH = 128 / LPC;                     // channels per CTA
+  constexpr int NP = NPT * LPC;                     // padded state size
+  __shared__ float sB[TC][NP], sC[TC][NP], sDt[TC][CH], sU[TC][CH], sZ[TC][CH], sY[TC][CH];
+  const int b = blockIdx.y;
+  const int q0 = p.cu_q ? p.cu_q[b] : b;
+  const int n = p.cu_q ? p.cu_q[b + 1] - q0 : 1;
+  if (n <= 0) return;
+  const int C = p.C, N = p.N;
+  const int tid = threadIdx.x, cl = tid / LPC, ks = tid % LPC;
+  const int c0 = blockIdx.x * CH, c = c0 + cl;
+  const bool live = c < C;
+  const bool fresh = p.seq_lens[b] - n == 0;
+  float* st = p.state + ((size_t)p.req_slots[b] * C + (live ? c : 0)) * N;
+  float S[NPT], A[NPT];
+#pragma unroll
+  for (int r = 0; r < NPT; ++r) {
+    const int i = ks * NPT + r;
+    const bool ok = live && i < N;
+    S[r] = (ok && !fresh) ? st[i] : 0.f;
+    A[r] = ok ? -expf(p.A_log[(size_t)c * N + i]) : 0.f;
+  }
+  const float dskip = (p.D && live) ? p.D[c] : 0.f;
+  const TBC* Bg = reinterpret_cast<const TBC*>(p.Bm);
+  const TBC* Cg = reinterpret_cast<const TBC*>(p.Cm);
+  const TZ* zg = reinterpret_cast<const TZ*>(p.z);
+  TO* og = reinterpret_cast<TO*>(p.out);
+  const int cw = min(CH, C - c0);                   // live channels of this CTA
+  for (int t0 = 0; t0 < n; t0 += TC) {
+    const int tc = min(TC, n - t0);
+    __syncthreads();                                // the previous chunk's rows are out
+    for (int idx = tid; idx < tc * NP; idx += 128) {
+      const int tt = idx / NP, i = idx - tt * NP;
+      const size_t row = (size_t)(q0 + t0 + tt) * p.ldbc;
+      sB[tt][i] = i < N ? m1_ld<TBC>(Bg + row + i) : 0.f;
+      sC[tt][i] = i < N ? m1_ld<TBC>(Cg + row + i) : 0.f;
+    }
+    for (int idx = tid; idx < tc * CH; idx += 128) {
+      const int tt = idx / CH, k = idx - tt * CH;
+      const size_t tok = (size_t)(q0 + t0 + tt);
+      const bool ok = k < cw;
+      const float raw = ok ? p.dt_raw[tok * p.lddt + c0 + k] + ((p.dt_bias) ? p.dt_bias[c0 + k] : 0.f) : 0.f;
+      sDt[tt][k] = raw > 20.f ? raw : log1pf(expf(raw));
+      sU[tt][k] = ok ? p.u[tok * C + c0 + k] : 0.f;
+      sZ[tt][k] = (ok && zg) ? m1_ld<TZ>(zg + tok * p.ldz + c0 + k) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < tc; ++tt) {
+      const float dt = sDt[tt][cl], uv = sU[tt][cl];
+      const float dbu = dt * uv;
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < NPT; ++r) {
+        const int i = ks * NPT + r;
+        const float da = sizeof(TO) == 4 ? expf(dt * A[r]) : __expf(dt * A[r]);
+        S[r] = da * S[r] + dbu * sB[tt][i];
+        acc += S[r] * sC[tt][i];
+      }
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (ks == 0) sY[tt][cl] = acc + dskip * uv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < tc * CH; idx += 128) {
+      const int tt = idx / CH, k = idx - tt * CH;
+      if (k < cw) {
+        float y = sY[tt][k];
+        if (zg) {
+          const float zz = sZ[tt][k];
+          y *= zz / (1.f + expf(-zz));
+        }
+        m1_st<TO>(og + (size_t)(q0 + t0 + tt) * C + c0 + k, y);
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const int i = ks * NPT + r;
+      if (i < N) st[i] = S[r];
+    }
+  }
+}
+
+template <typename TBC, typename TZ, typename TO, int NPT, int LPC>
+void launch_m1(const Mamba1Params& p, int B, cudaStream_t stream) {
+  constexpr int CH = 128 / LPC;
+  mamba1_scan_kernel<TBC, TZ, TO, NPT, LPC, 16><<<dim3((p.C + CH - 1) / CH, B), 128, 0, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+template <typename TBC, typename TZ, typename TO>
+void dispatch_m1(const Mamba1Params& p, int B, cudaStream_t stream) {
+  const int N = p.N;
+  if (N <= 4) launch_m1<TBC, TZ, TO, 4, 1>(p, B, stream);
+  else if (N <= 8) launch_m1<TBC, TZ, TO, 4, 2>(p, B, stream);
+  else if (N <= 16) launch_m1<TBC, TZ, TO, 4, 4>(p, B, stream);
+  else if (N <= 32) launch_m1<TBC, TZ, TO, 4, 8>(p, B, stream);
+  else if (N <= 64) launch_m1<TBC, TZ, TO, 8, 8>(p, B, stream);
+  else if (N <= 128) launch_m1<TBC, TZ, TO, 8, 16>(p, B, stream);
+  else launch_m1<TBC, TZ, TO, 8, 32>(p, B, stream);
+}
+
+template <typename TBC, typename TZ>
+void dispatch_m1_out(const Mamba1Params& p, int B, bool out_bf16, cudaStream_t stream) {
+  if (out_bf16) dispatch_m1<TBC, TZ, __nv_bfloat16>(p, B, stream);
+  else dispatch_m1<TBC, TZ, float>(p, B, stream);
+}
+
+}  // namespace
+
+void mamba1_scan(const float* u, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log, const void* Bm, const void* Cm, int ldbc, bool bc_bf16,
+                 const float* D, const void* z, int ldz, bool z_bf16, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int C,
+                 int N, void* out, bool out_bf16, cudaStream_t stream) {
+  if (B <= 0 || C <= 0) return;
+  if (N > 256 || B > 65535) throw std::runtime_error("sglb mamba1_scan: state size up to 256");
+  Mamba1Params p;
+  p.u = u; p.dt_raw = dt_raw; p.lddt = lddt; p.dt_bias = dt_bias; p.A_log = A_log; p.Bm = Bm; p.Cm = Cm; p.ldbc = ldbc; p.D = D; p.z = z; p.ldz = ldz;
+  p.state = state; p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.out = out; p.C = C; p.N = N;
+  if (bc_bf16) {
+    if (z_bf16) dispatch_m1_out<__nv_bfloat16, __nv_bfloat16>(p, B, out_bf16, stream);
+    else dispatch_m1_out<__nv_bfloat16, float>(p, B, out_bf16, stream);
+  } else {
+    if (z_bf16) dispatch_m1_out<float, __nv_bfloat16>(p, B, out_bf16, stream);
+    else dispatch_m1_out<float, float>(p, B, out_bf16, stream);
+  }
 }
 
 }  // namespace sglb

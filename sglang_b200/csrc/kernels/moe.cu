@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(256) moe_identity_shared_combine_kernel(T* __r
                                                                           const T* __restrict__ shared, const float* __restrict__ gate, int W) {
   const size_t base = (size_t)blockIdx.x * W;
   const float iw = ident ? ident[blockIdx.x] : 0.f;
-  const float sg = shared ? 1.f / (1.f + expf(-gate[blockIdx.x])) : 0.f;
+  const float sg = shared ? (gate ? 1.f / (1.f + expf(-gate[blockIdx.x])) : 1.f) : 0.f;          // no gate: the shared output joins as it is
   for (int c = threadIdx.x; c < W; c += 256) {
     float v = mc_ld<T>(y + base + c);
     if (ident) v += iw * mc_ld<T>(h + base + c);

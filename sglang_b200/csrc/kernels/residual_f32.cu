@@ -1,7 +1,8 @@
 // fp32 residual stream helpers.
 //
 //   add_rmsnorm_f32 : residual (fp32, in place) += delta (bf16 | fp32 | none); out = residual / rms(residual) * (w | 1 + w) in bf16 | fp32.
-//                     One block per row; the sum, the mean of squares and the scaling are fp32, eps sits inside the root.
+//                     One block per row; the sum, the mean of squares and the scaling are fp32, eps sits inside the root.  The weight is a
+//                     vector or one number for all coordinates.
 //   clamped_glu     : [gate | up] halves -> min(g, limit) * sigmoid(alpha * g) * (clamp(u, -limit, limit) + 1), fp32 math.
 #include <stdexcept>
 
@@ -20,7 +21,7 @@ template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p,
 
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256) add_rmsnorm_f32_kernel(float* __restrict__ res, const TD* __restrict__ delta, const TO* __restrict__ w,
-                                                              TO* __restrict__ out, int H, float eps, int zero_centred) {
+                                                              TO* __restrict__ out, int H, float eps, int zero_centred, int ws) {
   __shared__ float red[8];
   __shared__ float s_rs;
   float* r = res + (size_t)blockIdx.x * H;
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_f32_kernel(float* __restrict_
   const float rs = s_rs;
   TO* o = out + (size_t)blockIdx.x * H;
   for (int i = threadIdx.x; i < H; i += 256) {          // each thread re-reads exactly the elements it wrote
-    float wv = ldf<TO>(w + i);
+    float wv = ldf<TO>(w + i * ws);                   // ws = 0: one gain for all coordinates
     if (zero_centred) wv += 1.f;
     stf<TO>(o + i, r[i] * rs * wv);
   }
@@ -93,10 +94,12 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
 }
 
 // residual += rmsnorm(delta) * (1 + post_w);  out = rmsnorm(residual) * (1 + w): the post-norm of a branch, the residual add and the next
-// pre-norm of a sandwich-normed block in one pass over the row
+// pre-norm of a sandwich-normed block in one pass over the row.  ``one`` = 1 for weights stored around zero, 0 for plain weights; a weight
+// stride of 0 means one gain for all coordinates.
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256) postnorm_add_rmsnorm_f32_kernel(float* __restrict__ res, const TD* __restrict__ delta, const TO* __restrict__ post_w,
-                                                                       const TO* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+                                                                       const TO* __restrict__ w, TO* __restrict__ out, int H, float eps, float one,
+                                                                       int wsp, int ws) {
   __shared__ float red[8];
   float* r = res + (size_t)blockIdx.x * H;
   const TD* d = delta + (size_t)blockIdx.x * H;
@@ -108,19 +111,20 @@ __global__ void __launch_bounds__(256) postnorm_add_rmsnorm_f32_kernel(float* __
   const float rd = 1.0f / sqrtf(block_sum_256(sd, red) / (float)H + eps);
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += 256) {
-    const float v = r[i] + ldf<TD>(d + i) * rd * (1.f + ldf<TO>(post_w + i));
+    const float v = r[i] + ldf<TD>(d + i) * rd * (one + ldf<TO>(post_w + i * wsp));
     r[i] = v;
     ss += v * v;
   }
   const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)H + eps);
   TO* o = out + (size_t)blockIdx.x * H;
-  for (int i = threadIdx.x; i < H; i += 256) stf<TO>(o + i, r[i] * rs * (1.f + ldf<TO>(w + i)));          // each thread re-reads what it wrote
+  for (int i = threadIdx.x; i < H; i += 256) stf<TO>(o + i, r[i] * rs * (one + ldf<TO>(w + i * ws)));      // each thread re-reads what it wrote
 }
 
-// x fp32 [T, C] in ``groups`` equal parts: part / sqrt(mean(part^2) + eps) * w; grid (T, groups)
+// x fp32 [T, C] in ``groups`` equal parts: part / sqrt(mean(part^2) + eps) * w [* sigmoid(gate)] * out_scale; grid (T, groups); gate and out are
+// rows of ldg / ldo elements
 template <typename TO>
 __global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* __restrict__ x, const TO* __restrict__ w, TO* __restrict__ out, int C, int per,
-                                                              float eps) {
+                                                              float eps, const TO* __restrict__ gate, int ldg, int ldo, float out_scale) {
   __shared__ float red[8];
   const size_t base = (size_t)blockIdx.x * C + (size_t)blockIdx.y * per;
   float ss = 0.f;
@@ -128,8 +132,15 @@ __global__ void __launch_bounds__(256) grouped_rmsnorm_kernel(const float* __res
     const float v = x[base + i];
     ss += v * v;
   }
-  const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)per + eps);
-  for (int i = threadIdx.x; i < per; i += 256) stf<TO>(out + base + i, x[base + i] * rs * ldf<TO>(w + blockIdx.y * per + i));
+  const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)per + eps) * out_scale;
+  const int c0 = blockIdx.y * per;
+  TO* o = out + (size_t)blockIdx.x * ldo + c0;
+  const TO* gr = gate ? gate + (size_t)blockIdx.x * ldg + c0 : nullptr;
+  for (int i = threadIdx.x; i < per; i += 256) {
+    float v = x[base + i] * rs * ldf<TO>(w + c0 + i);
+    if (gr) v *= 1.f / (1.f + expf(-ldf<TO>(gr + i)));
+    stf<TO>(o + i, v);
+  }
 }
 
 // the same with one warp per (row, part): a CTA of 8 warps walks the parts of its row (many small parts: no CTA-wide barrier, 16-byte loads)
@@ -161,56 +172,60 @@ __global__ void __launch_bounds__(256) grouped_rmsnorm_warp_kernel(const float* 
 }  // namespace
 
 void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
-                              int H, float eps, cudaStream_t stream) {
+                              int H, float eps, bool zero_centred, int wsp, int ws, cudaStream_t stream) {
   if (T <= 0) return;
   using bf = __nv_bfloat16;
+  const float one = zero_centred ? 1.f : 0.f;
   if (out_bf16) {
     if (delta_bf16)
-      postnorm_add_rmsnorm_f32_kernel<bf, bf><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps);
+      postnorm_add_rmsnorm_f32_kernel<bf, bf><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps, one, wsp, ws);
     else
-      postnorm_add_rmsnorm_f32_kernel<float, bf><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps);
+      postnorm_add_rmsnorm_f32_kernel<float, bf><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const bf*)post_w, (const bf*)w, (bf*)out, H, eps, one, wsp, ws);
   } else {
     if (delta_bf16)
-      postnorm_add_rmsnorm_f32_kernel<bf, float><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const float*)post_w, (const float*)w, (float*)out, H, eps);
+      postnorm_add_rmsnorm_f32_kernel<bf, float><<<T, 256, 0, stream>>>(residual, (const bf*)delta, (const float*)post_w, (const float*)w, (float*)out, H, eps, one, wsp, ws);
     else
       postnorm_add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)post_w, (const float*)w,
-                                                                           (float*)out, H, eps);
+                                                                           (float*)out, H, eps, one, wsp, ws);
   }
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
-void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, cudaStream_t stream) {
+void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, const void* gate, int ldg, int ldo,
+                     float out_scale, cudaStream_t stream) {
   if (T <= 0) return;
   if (groups <= 0 || C % groups || groups > 65535) throw std::runtime_error("sglb grouped_rmsnorm: the width must split into equal parts");
   const int per = C / groups;
-  if (groups >= 4 && per % 4 == 0 && per <= 4096 && ((uintptr_t)x % 16) == 0) {
+  if (!gate && ldo == C && out_scale == 1.f && groups >= 4 && per % 4 == 0 && per <= 4096 && ((uintptr_t)x % 16) == 0) {
     if (out_bf16) grouped_rmsnorm_warp_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, per, groups, eps);
     else grouped_rmsnorm_warp_kernel<float><<<T, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, per, groups, eps);
     SGLB_CUDA_CHECK(cudaGetLastError());
     return;
   }
   dim3 g(T, groups);
-  if (out_bf16) grouped_rmsnorm_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, C / groups, eps);
-  else grouped_rmsnorm_kernel<float><<<g, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, C / groups, eps);
+  if (out_bf16)
+    grouped_rmsnorm_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, C, per, eps, (const __nv_bfloat16*)gate, ldg,
+                                                                 ldo, out_scale);
+  else grouped_rmsnorm_kernel<float><<<g, 256, 0, stream>>>(x, (const float*)w, (float*)out, C, per, eps, (const float*)gate, ldg, ldo, out_scale);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
 void add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* w, void* out, bool out_bf16, int T, int H, float eps,
-                     bool zero_centred, cudaStream_t stream) {
+                     bool zero_centred, int ws, cudaStream_t stream) {
   if (T <= 0) return;
   const int z = zero_centred ? 1 : 0;
   if (out_bf16) {
     if (delta_bf16)
       add_rmsnorm_f32_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w,
-                                                                                  (__nv_bfloat16*)out, H, eps, z);
+                                                                                  (__nv_bfloat16*)out, H, eps, z, ws);
     else
       add_rmsnorm_f32_kernel<float, __nv_bfloat16><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, H,
-                                                                          eps, z);
+                                                                          eps, z, ws);
   } else {
     if (delta_bf16)
-      add_rmsnorm_f32_kernel<__nv_bfloat16, float><<<T, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (const float*)w, (float*)out, H, eps, z);
+      add_rmsnorm_f32_kernel<__nv_bfloat16, float><<<T, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (const float*)w, (float*)out, H, eps, z, ws);
     else
-      add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)w, (float*)out, H, eps, z);
+      add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)w, (float*)out, H, eps, z, ws);
   }
   SGLB_CUDA_CHECK(cudaGetLastError());
 }

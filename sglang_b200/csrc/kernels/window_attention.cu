@@ -5,6 +5,12 @@
 //                         k heads go to the first G*D columns of the key plane's row, v to the first G*Dv columns of the value plane's row.
 //   window_attention    : s_ij = cap * tanh(q_i . k_j * scale / cap) - slope_h * (i - j), visible for 0 <= i - j < window;
 //                         p_ij = exp(s_ij) / (exp(sink_h) + sum_j' exp(s_ij')); o_i = sum_j p_ij v_j.
+//                         Options: the sequence's first ``keep_first`` positions stay visible behind the window (their tiles are walked before
+//                         the window's); the bias is slope_h * ln(1 + rate_h * (i - j)) instead of linear; the output is multiplied by
+//                         sigmoid(gate) per head or per element and by a constant in the epilogue, and may be a column block of a wider buffer.
+//   attention_prepare   : per token, q and k RMS-normed over their whole projection times a weight, the first coordinates of every head
+//                         rotated by position (pairs half a rotary width apart), v blended with another layer's values, k / v rows to the cache.
+//   sigmoid_gate        : o[:, :, :Dv] * sigmoid(gate) * constant, for attention kernels without a gate epilogue.
 //
 // window_attention mapping: one CTA per (tile of queries, chunk of the heads that share a key head, request): 32 rows = QT queries x HC heads.
 // Key tiles of 64 positions are gathered through the page table into shared memory as fp32 with 16-byte global loads where the sizes allow
@@ -81,6 +87,10 @@ struct WinAttnParams {
   const int* page_table; int pt_stride; int page_size;
   const int* req_slots; const int* seq_lens; const int* cu_q;
   const float* slopes; const float* sinks;
+  const float* log_rates;                      // non-null: the bias is slopes_h * ln(1 + log_rates_h * distance)
+  const void* gate; int ldg; int gate_per_head; // non-null: output times sigmoid(gate[t, h]) or sigmoid(gate[t, h * Dv + c])
+  int ldo; float out_scale;                    // output rows of ldo elements; everything times out_scale
+  int keep_first;                              // with a window: positions < keep_first stay visible
   int H, G, HG, HC, nchunks, QT, D, Dp, Dv;
   int Dq, hsk, hsv;                            // head strides of q and of the key / value rows (>= D, D, Dv: padded layouts)
   float scale, softcap; int window;
@@ -130,7 +140,7 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
   }
   // ---- per-row constants and online soft-max state (the sink is the first term: max = sink, sum = 1)
   const int r0 = warp * 4;
-  float m[4], l[4], slope[4], O[4][CV];
+  float m[4], l[4], slope[4], rate[4], O[4][CV];
   int qpos[4];
   bool rowok[4];
 #pragma unroll
@@ -140,16 +150,20 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
     const int h = hbase + (rowok[r] ? hc : 0);
     qpos[r] = pos0 + qi;
     slope[r] = p.slopes ? p.slopes[h] : 0.f;
+    rate[r] = p.log_rates ? p.log_rates[h] : 0.f;
     m[r] = p.sinks ? p.sinks[h] : -INFINITY;
     l[r] = p.sinks ? 1.f : 0.f;
 #pragma unroll
     for (int c = 0; c < CV; ++c) O[r][c] = 0.f;
   }
   const int klo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int khi = pos0 + nq;                            // one past the last key any query of the tile sees
+  const int kend = pos0 + nq;                           // one past the last key any query of the tile sees
+  const int nkeep = min(p.keep_first, klo);             // kept first positions that lie before the window: a segment of their own
   const int* pt = p.page_table + (size_t)p.req_slots[b] * p.pt_stride;
   const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
-  for (int kt = klo; kt < khi; kt += WA_KT) {
+  for (int seg = nkeep > 0 ? 0 : 1; seg < 2; ++seg) {
+  const int kbeg = seg == 0 ? 0 : klo, khi = seg == 0 ? nkeep : kend;
+  for (int kt = kbeg; kt < khi; kt += WA_KT) {
     __syncthreads();                                    // everyone is done with the previous tile (and sQ is written)
     if (tid < WA_KT) {
       const int j = kt + tid;
@@ -222,8 +236,9 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
         const int dist = qpos[r] - j;
         float v = acc[kk][r];
         if (p.softcap > 0.f) v = p.softcap * tanhf(v * inv_cap);
-        v -= slope[r] * (float)dist;
-        const bool vis = rowok[r] && dist >= 0 && (p.window <= 0 || dist < p.window);
+        if (p.log_rates) v -= slope[r] * log1pf(rate[r] * (float)max(dist, 0));
+        else v -= slope[r] * (float)dist;
+        const bool vis = rowok[r] && j < khi && dist >= 0 && (p.window <= 0 || dist < p.window || j < p.keep_first);
         s[kk] = vis ? v : -INFINITY;
       }
       const float mt = warp_max(fmaxf(s[0], s[1]));
@@ -255,17 +270,27 @@ __global__ void __launch_bounds__(WA_NT) window_attention_kernel(const WinAttnPa
     }
     __syncwarp();
   }
+  }
   T* og = reinterpret_cast<T*>(p.out);
+  const T* gg = reinterpret_cast<const T*>(p.gate);
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     if (!rowok[r]) continue;
     const int qi = (r0 + r) / HC, hc = (r0 + r) - qi * HC;
-    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-    T* dst = og + ((size_t)(q0 + qt0 + qi) * p.H + hbase + hc) * Dv;
+    const size_t tok = (size_t)(q0 + qt0 + qi);
+    const int h = hbase + hc;
+    float inv = (l[r] > 0.f ? 1.f / l[r] : 0.f) * p.out_scale;
+    const T* grow = gg ? gg + tok * p.ldg : nullptr;
+    if (grow && p.gate_per_head) inv *= 1.f / (1.f + expf(-wa_ld<T>(grow + h)));
+    T* dst = og + tok * p.ldo + (size_t)h * Dv;
 #pragma unroll
     for (int c = 0; c < CV; ++c) {
       const int col = lane + 32 * c;
-      if (col < Dv) wa_st<T>(dst + col, O[r][c] * inv);
+      if (col < Dv) {
+        float v = O[r][c] * inv;
+        if (grow && !p.gate_per_head) v *= 1.f / (1.f + expf(-wa_ld<T>(grow + (size_t)h * Dv + col)));
+        wa_st<T>(dst + col, v);
+      }
     }
   }
 }
@@ -301,7 +326,119 @@ __global__ void __launch_bounds__(128) sink_gate_kernel(const __nv_bfloat16* __r
   for (int i = threadIdx.x; i < Dv; i += 128) dst[i] = __float2bfloat16(__bfloat162float(src[i]) * gte);
 }
 
+// out[t, h * Dv + c] = o[t, h, c] * sigmoid(gate) * scale, c < Dv: gate [t, h] (per head) or [t, h * Dv + c]; o rows of ldo_in elements per head
+template <typename T>
+__global__ void __launch_bounds__(128) sigmoid_gate_kernel(const T* __restrict__ o, int hs, const T* __restrict__ gate, int ldg, int per_head, int H, int Dv,
+                                                           float scale, T* __restrict__ out, int ldo) {
+  const int t = blockIdx.x / H, h = blockIdx.x - t * H;
+  const T* src = o + (size_t)blockIdx.x * hs;
+  const T* g = gate + (size_t)t * ldg;
+  T* dst = out + (size_t)t * ldo + (size_t)h * Dv;
+  const float gh = per_head ? scale / (1.f + expf(-wa_ld<T>(g + h))) : 0.f;
+  for (int i = threadIdx.x; i < Dv; i += 128) {
+    const float m = per_head ? gh : scale / (1.f + expf(-wa_ld<T>(g + (size_t)h * Dv + i)));
+    wa_st<T>(dst + i, wa_ld<T>(src + i) * m);
+  }
+}
+
+struct PrepParams {
+  const void* qkv; int ld;                     // rows [q (H*D) | k (G*D) | v (G*Dv) | ...]
+  int H, G, D, Dv;
+  const int* positions;
+  const void* qw; const void* kw; float eps;   // projection-wide RMS norm weights (null: no norm)
+  const float* inv_freq; int half;             // rotary frequencies (null: no rotation); pairs (i, i + half), i < half
+  const void* v_first; int ldvf; float lam;    // values to blend with (null: none)
+  void* kc; void* vc; size_t ldc; const int* loc;
+  void* q_out; int Dq, hsk, hsv;               // head strides of q, key rows, value rows (>= D, D, Dv: zero padding behind the values)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_prepare_kernel(const PrepParams p) {
+  __shared__ float red[8];
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  const T* row = reinterpret_cast<const T*>(p.qkv) + (size_t)t * p.ld;
+  const size_t slot = (size_t)p.loc[t];
+  const int nq = p.H * p.D, nk = p.G * p.D;
+  float rq = 1.f, rk = 1.f;
+  if (p.qw) {                                   // mean of squares over the whole q projection, then the whole k projection
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < nq; i += 128) { const float v = wa_ld<T>(row + i); sq += v * v; }
+    for (int i = tid; i < nk; i += 128) { const float v = wa_ld<T>(row + nq + i); sk += v * v; }
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    if ((tid & 31) == 0) { red[tid >> 5] = sq; red[4 + (tid >> 5)] = sk; }
+    __syncthreads();
+    rq = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)nq + p.eps);
+    rk = 1.0f / sqrtf((red[4] + red[5] + red[6] + red[7]) / (float)nk + p.eps);
+  }
+  const float pos = (float)p.positions[t];
+  const T* qw = reinterpret_cast<const T*>(p.qw);
+  const T* kw = reinterpret_cast<const T*>(p.kw);
+  T* qo = reinterpret_cast<T*>(p.q_out) + (size_t)t * p.H * p.Dq;
+  T* ko = reinterpret_cast<T*>(p.kc) + slot * p.ldc;
+  T* vo = reinterpret_cast<T*>(p.vc) + slot * p.ldc;
+  const int half = p.inv_freq ? p.half : 0;
+  // q heads then k heads: element (head, i) of the padded destination
+  const int total = p.H * p.Dq + p.G * p.hsk;
+  for (int idx = tid; idx < total; idx += 128) {
+    const bool isq = idx < p.H * p.Dq;
+    const int rel = isq ? idx : idx - p.H * p.Dq;
+    const int hs = isq ? p.Dq : p.hsk;
+    const int hd = rel / hs, i = rel - hd * hs;
+    T* dst = (isq ? qo : ko) + rel;
+    if (i >= p.D) { wa_st<T>(dst, 0.f); continue; }
+    const T* src = row + (isq ? 0 : nq) + hd * p.D;
+    const T* w = isq ? qw : kw;
+    const float r = isq ? rq : rk;
+    auto val = [&](int c) { const float v = wa_ld<T>(src + c) * r; return w ? v * wa_ld<T>(w + hd * p.D + c) : v; };
+    float v = val(i);
+    if (i < 2 * half) {
+      const int fi = i < half ? i : i - half;
+      float sn, cs;
+      sincosf(pos * p.inv_freq[fi], &sn, &cs);
+      const float other = val(i < half ? i + half : i - half);
+      v = i < half ? v * cs - other * sn : v * cs + other * sn;
+    }
+    wa_st<T>(dst, v);
+  }
+  const T* vs = row + nq + nk;
+  const T* vf = p.v_first ? reinterpret_cast<const T*>(p.v_first) + (size_t)t * p.ldvf : nullptr;
+  for (int idx = tid; idx < p.G * p.hsv; idx += 128) {
+    const int gh = idx / p.hsv, c = idx - gh * p.hsv;
+    float v = 0.f;
+    if (c < p.Dv) {
+      v = wa_ld<T>(vs + gh * p.Dv + c);
+      if (vf) v = (1.f - p.lam) * v + p.lam * wa_ld<T>(vf + gh * p.Dv + c);
+    }
+    wa_st<T>(vo + idx, v);
+  }
+}
+
 }  // namespace
+
+void sigmoid_gate(const void* o, int head_stride, const void* gate, int ldg, bool per_head, bool bf16, int T, int H, int Dv, float scale, void* out, int ldo,
+                  cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return;
+  if (bf16)
+    sigmoid_gate_kernel<__nv_bfloat16><<<T * H, 128, 0, stream>>>((const __nv_bfloat16*)o, head_stride, (const __nv_bfloat16*)gate, ldg, per_head ? 1 : 0, H, Dv,
+                                                                  scale, (__nv_bfloat16*)out, ldo);
+  else
+    sigmoid_gate_kernel<float><<<T * H, 128, 0, stream>>>((const float*)o, head_stride, (const float*)gate, ldg, per_head ? 1 : 0, H, Dv, scale, (float*)out, ldo);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, const void* q_norm_w, const void* k_norm_w,
+                       float eps, const float* inv_freq, int half, const void* v_first, int ldvf, float lam, void* kc, void* vc, size_t ldc, const int* loc,
+                       void* q_out, int pad, cudaStream_t stream) {
+  if (T <= 0) return;
+  PrepParams p;
+  p.qkv = qkv; p.ld = ld; p.H = H; p.G = G; p.D = D; p.Dv = Dv; p.positions = positions; p.qw = q_norm_w; p.kw = k_norm_w; p.eps = eps;
+  p.inv_freq = inv_freq; p.half = half; p.v_first = v_first; p.ldvf = ldvf; p.lam = lam; p.kc = kc; p.vc = vc; p.ldc = ldc; p.loc = loc; p.q_out = q_out;
+  p.Dq = pad > 0 ? pad : D; p.hsk = pad > 0 ? pad : D; p.hsv = pad > 0 ? pad : Dv;
+  if (bf16) attention_prepare_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
+  else attention_prepare_kernel<float><<<T, 128, 0, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
 
 void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream) {
   if (rows <= 0) return;
@@ -324,13 +461,16 @@ void qk_norm_cache_write(const void* qkv, int ld, bool bf16, int T, int H, int G
 
 void window_attention(const void* q, const void* kc, const void* vc, bool bf16, size_t ldc, int H, int G, int D, int Dv, const int* page_table,
                       int pt_stride, int page_size, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, float scale,
-                      float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, cudaStream_t stream) {
+                      float softcap, int window, const float* slopes, const float* sinks, void* out, int pad, int keep_first, const float* log_rates,
+                      const void* gate, int ldg, bool gate_per_head, int ldo, float out_scale, cudaStream_t stream) {
   if (B <= 0 || max_q_len <= 0) return;
   if (D > 256 || Dv > 256 || B > 65535 || H % G) throw std::runtime_error("sglb window_attention: head sizes up to 256, heads a multiple of key heads");
   WinAttnParams p;
   p.q = q; p.kc = kc; p.vc = vc; p.out = out; p.ldc = ldc;
   p.page_table = page_table; p.pt_stride = pt_stride; p.page_size = page_size;
   p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.slopes = slopes; p.sinks = sinks;
+  p.log_rates = slopes ? log_rates : nullptr; p.gate = gate; p.ldg = ldg; p.gate_per_head = gate_per_head ? 1 : 0; p.ldo = ldo; p.out_scale = out_scale;
+  p.keep_first = window > 0 ? std::max(0, keep_first) : 0;
   p.H = H; p.G = G; p.HG = H / G;
   p.HC = std::min(p.HG, WA_ROWS);
   p.nchunks = (p.HG + p.HC - 1) / p.HC;
