@@ -50,9 +50,9 @@ def parse_args():
                     help="instead of the default workload: Rirotar beside Qwen3-Next at equal size (engine prefill / decode) and its kernels beside "
                          "the like ops, one JSON line per measurement (sglang_b200/benchmark/hybrid_compare.py)")
     ap.add_argument("--hybrid-sizes", default="2048,4096", help="model widths of --hybrid-compare")
-    ap.add_argument("--hybrid-family", default="rirotar", choices=("rirotar", "zaparax"),
-                    help="which per-layer hybrid family --hybrid-compare measures: rirotar beside Qwen3-Next, or zaparax beside Nemotron-H "
-                         "(sglang_b200/benchmark/zaparax_compare.py)")
+    ap.add_argument("--hybrid-family", default="rirotar", choices=("rirotar", "zaparax", "resatar"),
+                    help="which per-layer hybrid family --hybrid-compare measures: rirotar beside Qwen3-Next, zaparax beside Nemotron-H "
+                         "(sglang_b200/benchmark/zaparax_compare.py), or resatar beside Jamba (sglang_b200/benchmark/resatar_compare.py)")
     return ap.parse_args()
 
 
@@ -201,6 +201,8 @@ def main() -> None:
     if args.hybrid_compare:
         if args.hybrid_family == "zaparax":
             from sglang_b200.benchmark.zaparax_compare import main as hybrid_main
+        elif args.hybrid_family == "resatar":
+            from sglang_b200.benchmark.resatar_compare import main as hybrid_main
         else:
             from sglang_b200.benchmark.hybrid_compare import main as hybrid_main
 

@@ -19,7 +19,7 @@ def _has(op: str) -> bool:
 
 
 def topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-    if router_logits.is_cuda and _has("moe_topk_softmax"):
+    if router_logits.is_cuda and _has("moe_topk_softmax") and router_logits.shape[1] <= 512 and top_k <= 32:
         T = router_logits.shape[0]
         w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
         ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
