@@ -831,6 +831,11 @@ class JambaForCausalLM(BambaForCausalLM):
         mx = next((b.mamba for b in self.model.all_layers if b.kind == "mamba"), None)
         return None if mx is None else MambaPool(self.model.num_mamba, slots, mx.Dn, mx.k, mx.Dn, 1, mx.N, _DT[self.cfg.dtype], device)
 
+    def dummy_checkpoint(self, cfg: ModelConfig, device, dtype, seed: int = 0, scale: float = 0.02):
+        """no synthetic checkpoint of its own (the inherited one describes Mamba-2 tensors): every parameter takes the loader's name-seeded
+        random init"""
+        return iter(())
+
     def load_weights(self, weights):
         from .llama import _load_stacked_bias
 
