@@ -471,12 +471,58 @@ __global__ void __launch_bounds__(256) activation_kernel(const TI* __restrict__ 
   }
 }
 
+// eight elements per thread, 16-byte accesses (n and ldx multiples of 8, 16-byte aligned bases)
+template <typename TI, typename TO, int ACT>
+__global__ void __launch_bounds__(256) activation_vec8_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n8) {
+  const size_t total = (size_t)T * n8;
+  for (size_t idx = blockIdx.x * (size_t)256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const size_t t = idx / n8;
+    const int i = (int)(idx - t * n8) * 8;
+    float v[8];
+    if constexpr (sizeof(TI) == 2) {
+      const U4 a = ld128(x + t * ldx + i);
+      v[0] = bf16_lo(a.x); v[1] = bf16_hi(a.x); v[2] = bf16_lo(a.y); v[3] = bf16_hi(a.y);
+      v[4] = bf16_lo(a.z); v[5] = bf16_hi(a.z); v[6] = bf16_lo(a.w); v[7] = bf16_hi(a.w);
+    } else {
+      const float4 a = *reinterpret_cast<const float4*>(x + t * ldx + i), b = *reinterpret_cast<const float4*>(x + t * ldx + i + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (ACT == 0) v[k] = v[k] / (1.f + expf(-v[k]));
+      else { const float c = 0.7978845608028654f * (v[k] + 0.044715f * v[k] * v[k] * v[k]); v[k] = 0.5f * v[k] * (1.f + tanhf(c)); }
+    }
+    TO* o = out + idx * 8;
+    if constexpr (sizeof(TO) == 2) {
+      st128(o, U4{pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7])});
+    } else {
+      *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+}
+
 void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, cudaStream_t stream) {
   if (T <= 0 || n <= 0) return;
+  using bf = __nv_bfloat16;
+  if (n % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const size_t tv = (size_t)T * (n / 8);
+    const size_t gv = (tv + 255) / 256;
+    const int gridv = (int)(gv < (size_t)(148 * 16) ? gv : (size_t)(148 * 16));
+#define SGLB_ACTV(TI, TO)                                                                                                        \
+  do {                                                                                                                           \
+    if (act == 0) activation_vec8_kernel<TI, TO, 0><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8);           \
+    else activation_vec8_kernel<TI, TO, 2><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8);                    \
+  } while (0)
+    if (x_bf16) { if (out_bf16) SGLB_ACTV(bf, bf); else SGLB_ACTV(bf, float); }
+    else { if (out_bf16) SGLB_ACTV(float, bf); else SGLB_ACTV(float, float); }
+#undef SGLB_ACTV
+    SGLB_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
   const size_t total = (size_t)T * n;
   const size_t gq = (total + 255) / 256;
   const int grid = (int)(gq < (size_t)(148 * 16) ? gq : (size_t)(148 * 16));
-  using bf = __nv_bfloat16;
 #define SGLB_ACT(TI, TO)                                                                                                   \
   do {                                                                                                                     \
     if (act == 0) activation_kernel<TI, TO, 0><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n);               \

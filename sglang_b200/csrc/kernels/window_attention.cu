@@ -414,6 +414,93 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(const PrepParams
   }
 }
 
+// two neighbouring elements at once (4-byte or 8-byte accesses)
+__device__ __forceinline__ float2 wa_ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 wa_ld2(const __nv_bfloat16* p) {
+  const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(bf16_lo(v), bf16_hi(v));
+}
+__device__ __forceinline__ void wa_st2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void wa_st2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(a, b); }
+
+// the same work two columns at a time: even head sizes, rotary half-width and strides.  A rotated item is the four numbers
+// (i, i + 1, i + half, i + half + 1) of a head: two angles, each pair rotated once; a tail item is two unrotated columns (or zero padding).
+template <typename T>
+__global__ void __launch_bounds__(128) attention_prepare_vec_kernel(const PrepParams p) {
+  __shared__ float red[8];
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  const T* row = reinterpret_cast<const T*>(p.qkv) + (size_t)t * p.ld;
+  const size_t slot = (size_t)p.loc[t];
+  const int nq = p.H * p.D, nk = p.G * p.D;
+  float rq = 1.f, rk = 1.f;
+  if (p.qw) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = 2 * tid; i < nq; i += 256) { const float2 v = wa_ld2(row + i); sq += v.x * v.x + v.y * v.y; }
+    for (int i = 2 * tid; i < nk; i += 256) { const float2 v = wa_ld2(row + nq + i); sk += v.x * v.x + v.y * v.y; }
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    if ((tid & 31) == 0) { red[tid >> 5] = sq; red[4 + (tid >> 5)] = sk; }
+    __syncthreads();
+    rq = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)nq + p.eps);
+    rk = 1.0f / sqrtf((red[4] + red[5] + red[6] + red[7]) / (float)nk + p.eps);
+  }
+  const float pos = (float)p.positions[t];
+  const T* qw = reinterpret_cast<const T*>(p.qw);
+  const T* kw = reinterpret_cast<const T*>(p.kw);
+  T* qo = reinterpret_cast<T*>(p.q_out) + (size_t)t * p.H * p.Dq;
+  T* ko = reinterpret_cast<T*>(p.kc) + slot * p.ldc;
+  T* vo = reinterpret_cast<T*>(p.vc) + slot * p.ldc;
+  const int half = p.inv_freq ? p.half : 0;
+  const int nrot = half / 2;                              // rotated items per head
+  const int per_q = nrot + (p.Dq - 2 * half) / 2, per_k = nrot + (p.hsk - 2 * half) / 2;
+  const int total = p.H * per_q + p.G * per_k;
+  for (int idx = tid; idx < total; idx += 128) {
+    const bool isq = idx < p.H * per_q;
+    const int rel = isq ? idx : idx - p.H * per_q;
+    const int per = isq ? per_q : per_k, hs = isq ? p.Dq : p.hsk;
+    const int hd = rel / per, it = rel - hd * per;
+    const T* src = row + (isq ? 0 : nq) + hd * p.D;
+    const T* w = isq ? qw : kw;
+    const float r = isq ? rq : rk;
+    T* dst = (isq ? qo : ko) + (size_t)hd * hs;
+    auto val2 = [&](int c) {
+      float2 v = wa_ld2(src + c);
+      v.x *= r; v.y *= r;
+      if (w) { const float2 ww = wa_ld2(w + hd * p.D + c); v.x *= ww.x; v.y *= ww.y; }
+      return v;
+    };
+    if (it < nrot) {
+      const int i = 2 * it;
+      const float2 a = val2(i), b = val2(i + half);
+      float s0, c0, s1, c1;
+      sincosf(pos * p.inv_freq[i], &s0, &c0);
+      sincosf(pos * p.inv_freq[i + 1], &s1, &c1);
+      wa_st2(dst + i, a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+      wa_st2(dst + i + half, b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    } else {
+      const int c = 2 * half + 2 * (it - nrot);
+      if (c < p.D) { const float2 v = val2(c); wa_st2(dst + c, v.x, v.y); }
+      else wa_st2(dst + c, 0.f, 0.f);
+    }
+  }
+  const T* vs = row + nq + nk;
+  const T* vf = p.v_first ? reinterpret_cast<const T*>(p.v_first) + (size_t)t * p.ldvf : nullptr;
+  const int hv2 = p.hsv / 2;
+  for (int idx = tid; idx < p.G * hv2; idx += 128) {
+    const int gh = idx / hv2, c = 2 * (idx - gh * hv2);
+    float2 v = make_float2(0.f, 0.f);
+    if (c < p.Dv) {
+      v = wa_ld2(vs + gh * p.Dv + c);
+      if (vf) {
+        const float2 f = wa_ld2(vf + gh * p.Dv + c);
+        v.x = (1.f - p.lam) * v.x + p.lam * f.x;
+        v.y = (1.f - p.lam) * v.y + p.lam * f.y;
+      }
+    }
+    wa_st2(vo + (size_t)gh * p.hsv + c, v.x, v.y);
+  }
+}
+
 }  // namespace
 
 void sigmoid_gate(const void* o, int head_stride, const void* gate, int ldg, bool per_head, bool bf16, int T, int H, int Dv, float scale, void* out, int ldo,
@@ -435,8 +522,17 @@ void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, 
   p.qkv = qkv; p.ld = ld; p.H = H; p.G = G; p.D = D; p.Dv = Dv; p.positions = positions; p.qw = q_norm_w; p.kw = k_norm_w; p.eps = eps;
   p.inv_freq = inv_freq; p.half = half; p.v_first = v_first; p.ldvf = ldvf; p.lam = lam; p.kc = kc; p.vc = vc; p.ldc = ldc; p.loc = loc; p.q_out = q_out;
   p.Dq = pad > 0 ? pad : D; p.hsk = pad > 0 ? pad : D; p.hsv = pad > 0 ? pad : Dv;
-  if (bf16) attention_prepare_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
-  else attention_prepare_kernel<float><<<T, 128, 0, stream>>>(p);
+  const size_t a2 = bf16 ? 4 : 8;          // bytes of a two-element access
+  auto al = [&](const void* q) { return q == nullptr || ((uintptr_t)q % a2) == 0; };
+  const bool vec = D % 2 == 0 && Dv % 2 == 0 && half % 2 == 0 && ld % 2 == 0 && ldc % 2 == 0 && p.Dq % 2 == 0 && p.hsk % 2 == 0 && p.hsv % 2 == 0 &&
+                   (v_first == nullptr || ldvf % 2 == 0) && al(qkv) && al(kc) && al(vc) && al(q_out) && al(v_first) && al(q_norm_w) && al(k_norm_w);
+  if (vec) {
+    if (bf16) attention_prepare_vec_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
+    else attention_prepare_vec_kernel<float><<<T, 128, 0, stream>>>(p);
+  } else {
+    if (bf16) attention_prepare_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
+    else attention_prepare_kernel<float><<<T, 128, 0, stream>>>(p);
+  }
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
