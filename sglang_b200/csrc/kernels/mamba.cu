@@ -483,8 +483,8 @@ void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt
 //   y <- y * silu(z).  State fp32 [slots, C, N]; a request whose cached length is zero starts from S = 0 whatever its slot holds.
 // Mapping: CTA = (block of CH channels, request), 128 threads; a channel's N states lie in the registers of LPC neighbouring lanes, NPT per
 // lane (A likewise: exp(A_log) is computed once per call); tokens are staged TC at a time through shared memory (B, C per state; dt, u, z
-// per channel), so the serial chain reads no global memory; the read-out is reduced over the channel's lanes with shuffles and leaves
-// through shared memory in rows.  Token order is fixed: a position's output is bit-identical however the prompt was cut or batched.
+// per channel), so the serial chain reads no global memory, and the next chunk's inputs are fetched into registers while the current one is
+// computed; the read-out is reduced over the channel's lanes with shuffles and leaves through shared memory in rows.  Token order is fixed: a position's output is bit-identical however the prompt was cut or batched.
 namespace {
 
 struct Mamba1Params {
@@ -521,12 +521,25 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
   const bool fresh = p.seq_lens[b] - n == 0;
   float* st = p.state + ((size_t)p.req_slots[b] * C + (live ? c : 0)) * N;
   float S[NPT], A[NPT];
+  const bool vec4 = (N % 4) == 0;                   // a lane's states are whole 16-byte groups (NPT is 4 or 8)
+  if (vec4) {
 #pragma unroll
-  for (int r = 0; r < NPT; ++r) {
-    const int i = ks * NPT + r;
-    const bool ok = live && i < N;
-    S[r] = (ok && !fresh) ? st[i] : 0.f;
-    A[r] = ok ? -expf(p.A_log[(size_t)c * N + i]) : 0.f;
+    for (int r = 0; r < NPT; r += 4) {
+      const int i = ks * NPT + r;
+      const bool ok = live && i < N;
+      const float4 sv = (ok && !fresh) ? *reinterpret_cast<const float4*>(st + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 av = ok ? *reinterpret_cast<const float4*>(p.A_log + (size_t)c * N + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[r] = sv.x; S[r + 1] = sv.y; S[r + 2] = sv.z; S[r + 3] = sv.w;
+      A[r] = ok ? -expf(av.x) : 0.f; A[r + 1] = ok ? -expf(av.y) : 0.f; A[r + 2] = ok ? -expf(av.z) : 0.f; A[r + 3] = ok ? -expf(av.w) : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < NPT; ++r) {
+      const int i = ks * NPT + r;
+      const bool ok = live && i < N;
+      S[r] = (ok && !fresh) ? st[i] : 0.f;
+      A[r] = ok ? -expf(p.A_log[(size_t)c * N + i]) : 0.f;
+    }
   }
   const float dskip = (p.D && live) ? p.D[c] : 0.f;
   const TBC* Bg = reinterpret_cast<const TBC*>(p.Bm);
@@ -534,25 +547,50 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
   const TZ* zg = reinterpret_cast<const TZ*>(p.z);
   TO* og = reinterpret_cast<TO*>(p.out);
   const int cw = min(CH, C - c0);                   // live channels of this CTA
+  constexpr int NBC = (TC * NP + 127) / 128;        // B (and C) values a thread fetches per chunk
+  constexpr int NCH = (TC * CH + 127) / 128;        // dt (and u, z) values a thread fetches per chunk
+  float rB[NBC], rC[NBC], rDt[NCH], rU[NCH], rZ[NCH];
+  auto fetch = [&](int t0) {                        // the chunk's inputs into registers: the loads fly while the previous chunk is computed
+    const int tc = min(TC, n - t0);
+#pragma unroll
+    for (int k = 0; k < NBC; ++k) {
+      const int idx = tid + k * 128, tt = idx / NP, i = idx - tt * NP;
+      const bool ok = tt < tc && i < N;
+      const size_t row = (size_t)(q0 + t0 + (ok ? tt : 0)) * p.ldbc;
+      rB[k] = ok ? m1_ld<TBC>(Bg + row + i) : 0.f;
+      rC[k] = ok ? m1_ld<TBC>(Cg + row + i) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int idx = tid + k * 128, tt = idx / CH, kk = idx - tt * CH;
+      const bool ok = tt < tc && kk < cw;
+      const size_t tok = (size_t)(q0 + t0 + (ok ? tt : 0));
+      rDt[k] = ok ? p.dt_raw[tok * p.lddt + c0 + kk] + (p.dt_bias ? p.dt_bias[c0 + kk] : 0.f) : 0.f;
+      rU[k] = ok ? p.u[tok * C + c0 + kk] : 0.f;
+      rZ[k] = (ok && zg) ? m1_ld<TZ>(zg + tok * p.ldz + c0 + kk) : 0.f;
+    }
+  };
+  fetch(0);
   for (int t0 = 0; t0 < n; t0 += TC) {
     const int tc = min(TC, n - t0);
     __syncthreads();                                // the previous chunk's rows are out
-    for (int idx = tid; idx < tc * NP; idx += 128) {
-      const int tt = idx / NP, i = idx - tt * NP;
-      const size_t row = (size_t)(q0 + t0 + tt) * p.ldbc;
-      sB[tt][i] = i < N ? m1_ld<TBC>(Bg + row + i) : 0.f;
-      sC[tt][i] = i < N ? m1_ld<TBC>(Cg + row + i) : 0.f;
+#pragma unroll
+    for (int k = 0; k < NBC; ++k) {
+      const int idx = tid + k * 128;
+      if (idx < TC * NP) { (&sB[0][0])[idx] = rB[k]; (&sC[0][0])[idx] = rC[k]; }
     }
-    for (int idx = tid; idx < tc * CH; idx += 128) {
-      const int tt = idx / CH, k = idx - tt * CH;
-      const size_t tok = (size_t)(q0 + t0 + tt);
-      const bool ok = k < cw;
-      const float raw = ok ? p.dt_raw[tok * p.lddt + c0 + k] + ((p.dt_bias) ? p.dt_bias[c0 + k] : 0.f) : 0.f;
-      sDt[tt][k] = raw > 20.f ? raw : log1pf(expf(raw));
-      sU[tt][k] = ok ? p.u[tok * C + c0 + k] : 0.f;
-      sZ[tt][k] = (ok && zg) ? m1_ld<TZ>(zg + tok * p.ldz + c0 + k) : 0.f;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int idx = tid + k * 128;
+      if (idx < TC * CH) {
+        const float raw = rDt[k];
+        (&sDt[0][0])[idx] = raw > 20.f ? raw : log1pf(expf(raw));
+        (&sU[0][0])[idx] = rU[k];
+        (&sZ[0][0])[idx] = rZ[k];
+      }
     }
     __syncthreads();
+    if (t0 + TC < n) fetch(t0 + TC);
     for (int tt = 0; tt < tc; ++tt) {
       const float dt = sDt[tt][cl], uv = sU[tt][cl];
       const float dbu = dt * uv;
@@ -581,7 +619,13 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
       }
     }
   }
-  if (live) {
+  if (live && vec4) {
+#pragma unroll
+    for (int r = 0; r < NPT; r += 4) {
+      const int i = ks * NPT + r;
+      if (i < N) *reinterpret_cast<float4*>(st + i) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+    }
+  } else if (live) {
 #pragma unroll
     for (int r = 0; r < NPT; ++r) {
       const int i = ks * NPT + r;
@@ -593,7 +637,8 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
 template <typename TBC, typename TZ, typename TO, int NPT, int LPC>
 void launch_m1(const Mamba1Params& p, int B, cudaStream_t stream) {
   constexpr int CH = 128 / LPC;
-  mamba1_scan_kernel<TBC, TZ, TO, NPT, LPC, 16><<<dim3((p.C + CH - 1) / CH, B), 128, 0, stream>>>(p);
+  constexpr int TC = NPT * LPC <= 64 ? 16 : (NPT * LPC <= 128 ? 8 : 4);          // tokens per staged chunk: the prefetch registers stay few
+  mamba1_scan_kernel<TBC, TZ, TO, NPT, LPC, TC><<<dim3((p.C + CH - 1) / CH, B), 128, 0, stream>>>(p);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
