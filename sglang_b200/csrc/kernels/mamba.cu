@@ -11,6 +11,8 @@
 //
 // Reference counterparts: kernels/aot/csrc/mamba/causal_conv1d.cu (fwd + update), layers/attention/mamba/ops/mamba_ssm.py
 // (selective_state_update Triton kernel); states indexed by request slot as in mem_cache/memory_pool.py MambaPool.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tma_host.h"
 
@@ -484,7 +486,9 @@ void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt
 // Mapping: CTA = (block of CH channels, request), 128 threads; a channel's N states lie in the registers of LPC neighbouring lanes, NPT per
 // lane (A likewise: exp(A_log) is computed once per call); tokens are staged TC at a time through shared memory (B, C per state; dt, u, z
 // per channel), so the serial chain reads no global memory, and the next chunk's inputs are fetched into registers while the current one is
-// computed; the read-out is reduced over the channel's lanes with shuffles and leaves through shared memory in rows.  Token order is fixed: a position's output is bit-identical however the prompt was cut or batched.
+// computed; the read-out is reduced over the channel's lanes with shuffles and leaves through shared memory in rows.  Token order is fixed;
+// how many states a lane holds (and so the order of the read-out's sum) follows the grid size, and single decode tokens take a kernel
+// without staging: a position's output depends on how the prompt was cut or batched by fp32 rounding only.
 namespace {
 
 struct Mamba1Params {
@@ -521,10 +525,10 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
   const bool fresh = p.seq_lens[b] - n == 0;
   float* st = p.state + ((size_t)p.req_slots[b] * C + (live ? c : 0)) * N;
   float S[NPT], A[NPT];
-  const bool vec4 = (N % 4) == 0;                   // a lane's states are whole 16-byte groups (NPT is 4 or 8)
+  const bool vec4 = NPT % 4 == 0 && (N % 4) == 0;   // a lane's states are whole 16-byte groups
   if (vec4) {
 #pragma unroll
-    for (int r = 0; r < NPT; r += 4) {
+    for (int r = 0; r + 3 < NPT; r += 4) {
       const int i = ks * NPT + r;
       const bool ok = live && i < N;
       const float4 sv = (ok && !fresh) ? *reinterpret_cast<const float4*>(st + i) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -621,7 +625,7 @@ __global__ void __launch_bounds__(128) mamba1_scan_kernel(const Mamba1Params p) 
   }
   if (live && vec4) {
 #pragma unroll
-    for (int r = 0; r < NPT; r += 4) {
+    for (int r = 0; r + 3 < NPT; r += 4) {
       const int i = ks * NPT + r;
       if (i < N) *reinterpret_cast<float4*>(st + i) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
     }
@@ -642,13 +646,92 @@ void launch_m1(const Mamba1Params& p, int B, cudaStream_t stream) {
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
+// fewer states per lane = more lanes and CTAs per channel block: taken (for the usual equal input / output types and small states) when the
+// grid would otherwise leave SMs idle — one long prompt is a serial chain per channel, so parallelism has to come from the state dimension
+template <typename TBC, typename TZ, typename TO, int LPC4>
+void launch_m1_small(const Mamba1Params& p, int B, cudaStream_t stream) {
+  if constexpr (std::is_same<TBC, TZ>::value && std::is_same<TBC, TO>::value) {
+    const long long ctas4 = (long long)((p.C + 128 / LPC4 - 1) / (128 / LPC4)) * B;          // CTAs with 4 states per lane
+    if (ctas4 < 600 && p.N > 2 * LPC4) {
+      if (ctas4 < 300 && LPC4 * 4 <= 32) launch_m1<TBC, TZ, TO, 1, LPC4 * 4>(p, B, stream);
+      else launch_m1<TBC, TZ, TO, 2, LPC4 * 2>(p, B, stream);
+      return;
+    }
+  }
+  launch_m1<TBC, TZ, TO, 4, LPC4>(p, B, stream);
+}
+
+// one token per request (decode): no staging.  A lane holds 4 states of its channel; a channel's LPC lanes sit in one warp; the state is read
+// and written with 16-byte accesses, everything else is a handful of scalars per lane.
+template <typename TBC, typename TZ, typename TO, int LPC>
+__global__ void __launch_bounds__(256) mamba1_decode_kernel(const Mamba1Params p) {
+  const int b = blockIdx.y;
+  const int gid = blockIdx.x * 256 + threadIdx.x;
+  const int c = gid / LPC, ks = gid - c * LPC;
+  const int C = p.C, N = p.N;
+  const bool live = c < C;
+  const int i = ks * 4;
+  const bool ok = live && i < N;
+  const bool fresh = p.seq_lens[b] - 1 == 0;
+  float* st = p.state + ((size_t)p.req_slots[b] * C + (live ? c : 0)) * N + (ok ? i : 0);
+  float4 S = make_float4(0.f, 0.f, 0.f, 0.f), A = S, Bv = S, Cv = S;
+  if (ok) {
+    if (!fresh) S = *reinterpret_cast<const float4*>(st);
+    A = *reinterpret_cast<const float4*>(p.A_log + (size_t)c * N + i);
+    const TBC* br = reinterpret_cast<const TBC*>(p.Bm) + (size_t)b * p.ldbc + i;
+    const TBC* cr = reinterpret_cast<const TBC*>(p.Cm) + (size_t)b * p.ldbc + i;
+    Bv = make_float4(m1_ld<TBC>(br), m1_ld<TBC>(br + 1), m1_ld<TBC>(br + 2), m1_ld<TBC>(br + 3));
+    Cv = make_float4(m1_ld<TBC>(cr), m1_ld<TBC>(cr + 1), m1_ld<TBC>(cr + 2), m1_ld<TBC>(cr + 3));
+  }
+  float dt = 0.f, u = 0.f;
+  if (live) {
+    const float raw = p.dt_raw[(size_t)b * p.lddt + c] + (p.dt_bias ? p.dt_bias[c] : 0.f);
+    dt = raw > 20.f ? raw : log1pf(expf(raw));
+    u = p.u[(size_t)b * C + c];
+  }
+  const float dbu = dt * u;
+  auto ex = [](float x) { return sizeof(TO) == 4 ? expf(x) : __expf(x); };
+  S.x = ex(-dt * expf(A.x)) * S.x + dbu * Bv.x;
+  S.y = ex(-dt * expf(A.y)) * S.y + dbu * Bv.y;
+  S.z = ex(-dt * expf(A.z)) * S.z + dbu * Bv.z;
+  S.w = ex(-dt * expf(A.w)) * S.w + dbu * Bv.w;
+  float acc = S.x * Cv.x + S.y * Cv.y + S.z * Cv.z + S.w * Cv.w;
+#pragma unroll
+  for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (ok) *reinterpret_cast<float4*>(st) = S;
+  if (live && ks == 0) {
+    float y = acc + (p.D ? p.D[c] : 0.f) * u;
+    if (p.z) {
+      const float zz = m1_ld<TZ>(reinterpret_cast<const TZ*>(p.z) + (size_t)b * p.ldz + c);
+      y *= zz / (1.f + expf(-zz));
+    }
+    m1_st<TO>(reinterpret_cast<TO*>(p.out) + (size_t)b * C + c, y);
+  }
+}
+
+template <typename TBC, typename TZ, typename TO, int LPC>
+void launch_m1_decode(const Mamba1Params& p, int B, cudaStream_t stream) {
+  const long long lanes = (long long)p.C * LPC;
+  mamba1_decode_kernel<TBC, TZ, TO, LPC><<<dim3((unsigned)((lanes + 255) / 256), B), 256, 0, stream>>>(p);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 template <typename TBC, typename TZ, typename TO>
 void dispatch_m1(const Mamba1Params& p, int B, cudaStream_t stream) {
   const int N = p.N;
+  if (p.cu_q == nullptr && N % 4 == 0 && N <= 128) {          // decode batches
+    if (N <= 4) launch_m1_decode<TBC, TZ, TO, 1>(p, B, stream);
+    else if (N <= 8) launch_m1_decode<TBC, TZ, TO, 2>(p, B, stream);
+    else if (N <= 16) launch_m1_decode<TBC, TZ, TO, 4>(p, B, stream);
+    else if (N <= 32) launch_m1_decode<TBC, TZ, TO, 8>(p, B, stream);
+    else if (N <= 64) launch_m1_decode<TBC, TZ, TO, 16>(p, B, stream);
+    else launch_m1_decode<TBC, TZ, TO, 32>(p, B, stream);
+    return;
+  }
   if (N <= 4) launch_m1<TBC, TZ, TO, 4, 1>(p, B, stream);
-  else if (N <= 8) launch_m1<TBC, TZ, TO, 4, 2>(p, B, stream);
-  else if (N <= 16) launch_m1<TBC, TZ, TO, 4, 4>(p, B, stream);
-  else if (N <= 32) launch_m1<TBC, TZ, TO, 4, 8>(p, B, stream);
+  else if (N <= 8) launch_m1_small<TBC, TZ, TO, 2>(p, B, stream);
+  else if (N <= 16) launch_m1_small<TBC, TZ, TO, 4>(p, B, stream);
+  else if (N <= 32) launch_m1_small<TBC, TZ, TO, 8>(p, B, stream);
   else if (N <= 64) launch_m1<TBC, TZ, TO, 8, 8>(p, B, stream);
   else if (N <= 128) launch_m1<TBC, TZ, TO, 8, 16>(p, B, stream);
   else launch_m1<TBC, TZ, TO, 8, 32>(p, B, stream);

@@ -91,7 +91,7 @@ def test_activation(kind, dtype):
         torch.testing.assert_close(got.cpu().float(), want, **_tol(od, (1e-5, 1e-6)))
 
 
-@pytest.mark.parametrize("C,N", [(256, 20), (7, 1), (33, 4), (20, 9), (130, 16), (64, 33), (12, 100), (5, 200)])
+@pytest.mark.parametrize("C,N", [(256, 20), (7, 1), (33, 4), (20, 9), (130, 16), (64, 33), (12, 100), (5, 200), (5000, 16), (2600, 12), (1300, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_selective_scan(C, N, dtype):
     _need()
