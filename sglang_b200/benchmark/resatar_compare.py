@@ -155,8 +155,19 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         keys = sum(min(i + 1, W) for i in range(S - Q, S))
         nbytes = q.numel() * 2 * 3 + B * min(S, W + Q) * Gk * Dh * 2 * 2
         ph = "prefill" if Q > 1 else "decode"
-        rec("window_attention (general kernel) with kept tokens, logarithmic bias, element gate", ph, f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} keep4", ms, nbytes,
+        rec("window_attention (general kernel: fp32 serving and head sizes beyond 128) with kept tokens, logarithmic bias, element gate", ph, f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} keep4", ms, nbytes,
             "paged_attention (tcgen05 / split-KV decode kernel, same window)", like, like_bytes=nbytes - q.numel() * 2, flops=4.0 * B * keys * H * Dh)
+        # the same window layer on the tcgen05 kernels (bf16 serving with heads up to 128 wide): window, kept tokens and logarithmic bias inside, gate pass behind
+
+        def window_tc():
+            o = ops.paged_attention(q, k4, v4, pt, slots, sl, cu, None if Q == 1 else ql, Q, ps, Dh ** -0.5, True, W, num_splits=ns, slopes=r1, log_rates=r2,
+                                    keep_first=4)
+            return ops.sigmoid_gate(o, ge, Dh)
+
+        ms1 = timer(window_tc)
+        rec("window attention on the tcgen05 kernels (kept tokens, logarithmic bias) + sigmoid_gate (element)", ph, f"B{B} S{S} q{Q} H{H} G{Gk} D{Dh} window{W} keep4 splits{ns}",
+            ms1, nbytes + q.numel() * 2 * 2, "paged_attention (tcgen05 / split-KV decode kernel, same window)", like, like_bytes=nbytes - q.numel() * 2,
+            flops=4.0 * B * keys * H * Dh)
         # rotary causal attention with a per-head gate: the tcgen05 kernels + the gate pass, beside the same kernels alone
         keys = sum(i + 1 for i in range(S - Q, S))
         nb2 = q.numel() * 2 * 2 + B * S * Gk * Dh * 2 * 2

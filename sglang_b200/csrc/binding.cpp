@@ -106,11 +106,17 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& 
               const at::Tensor& page_table, const at::Tensor& req_slots, const at::Tensor& seq_lens,
               c10::optional<at::Tensor> cu_q, c10::optional<at::Tensor> tok2req, int64_t max_q_len, int64_t page_size,
               int64_t num_splits, double scale, bool causal, int64_t window, double logit_cap, double k_scale,
-              double v_scale, int64_t impl, c10::optional<at::Tensor> tree_anc, c10::optional<at::Tensor> slopes) {
+              double v_scale, int64_t impl, c10::optional<at::Tensor> tree_anc, c10::optional<at::Tensor> slopes,
+              c10::optional<at::Tensor> log_rates, int64_t keep_first) {
   CHECK_CUDA(q); CHECK_BF16(q); CHECK_BF16(out); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
   TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2), "q must be [T, Hq, D] with packed heads");
-  TORCH_CHECK(out.is_contiguous() && k_cache.is_contiguous() && v_cache.is_contiguous());
-  TORCH_CHECK(k_cache.dim() == 3, "k_cache must be [slots, Hkv, D]");
+  TORCH_CHECK(k_cache.dim() == 3 && v_cache.dim() == 3, "k_cache must be [slots, Hkv, D]");
+  // the tcgen05 kernels read the caches through tensor maps: a layer may use the leading Hkv * D columns of wider pool rows
+  const bool tc_impl = impl == 0 || impl == 2;
+  const bool rows_ok = k_cache.stride(2) == 1 && k_cache.stride(1) == k_cache.size(2) && v_cache.strides() == k_cache.strides() &&
+                       k_cache.stride(0) >= k_cache.size(1) * k_cache.size(2);
+  TORCH_CHECK(out.is_contiguous() && (tc_impl ? rows_ok : (k_cache.is_contiguous() && v_cache.is_contiguous())), "attn_fwd: cache layout");
+  const int kv_stride = (int)k_cache.stride(0);
   const int T = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)k_cache.size(1);
   const int B = (int)req_slots.size(0);
   const bool fp8 = k_cache.scalar_type() == at::kFloat8_e4m3fn;
@@ -118,6 +124,11 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& 
   if (slopes.has_value())      // per-head distance bias (tcgen05 kernels only)
     TORCH_CHECK((impl == 0 || impl == 2) && slopes->scalar_type() == at::kFloat && slopes->is_contiguous() && slopes->numel() == Hq && causal,
                 "attn_fwd: slopes must be fp32 [Hq] on the tcgen05 kernels, causal");
+  if (log_rates.has_value())   // logarithmic form of the distance bias: slopes[h] * ln(1 + log_rates[h] * distance)
+    TORCH_CHECK(slopes.has_value() && log_rates->scalar_type() == at::kFloat && log_rates->is_contiguous() && log_rates->numel() == Hq && logit_cap <= 0.0,
+                "attn_fwd: log_rates must be fp32 [Hq], given with slopes and without a soft cap");
+  if (keep_first > 0)          // kept first tokens of a window (tcgen05 kernels only)
+    TORCH_CHECK((impl == 0 || impl == 2) && causal && !tree_anc.has_value(), "attn_fwd: kept first tokens need the tcgen05 kernels, causal");
   if (impl == 0 || impl == 2) {
     TORCH_CHECK(!fp8, "tcgen05 attention: fp8 KV cache not yet supported (use impl=1)");
     if (num_splits > 1) TORCH_CHECK(part_o.has_value() && part_lse.has_value(), "split-KV needs workspaces");
@@ -142,7 +153,8 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& 
       sglb::attn_decode_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), opt_mptr<float>(lse), opt_mptr<float>(part_o),
                            opt_mptr<float>(part_lse), page_table.data_ptr<int>(), (int)page_table.stride(0), req_slots.data_ptr<int>(),
                            seq_lens.data_ptr<int>(), B, (int)q.stride(0), Hq, Hkv, D, (int)k_cache.size(0), (int)page_size, (int)num_splits,
-                           (float)scale, (int)window, (float)logit_cap, sched_ptr, num_sms(), cur_stream(), opt_ptr<float>(slopes));
+                           (float)scale, (int)window, (float)logit_cap, sched_ptr, num_sms(), cur_stream(), opt_ptr<float>(slopes), opt_ptr<float>(log_rates),
+                           (int)keep_first, kv_stride);
       count(num_splits > 1 ? 2 : 1);
       return;
     }
@@ -152,7 +164,8 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& 
                       (int)page_table.stride(0), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, T,
                       (int)q.stride(0), (int)max_q_len, Hq, Hkv, D, (int)k_cache.size(0), (int)page_size, (int)num_splits,
                       (float)scale, causal ? 1 : 0, (int)window, (float)logit_cap, sched_ptr, num_sms(), cur_stream(),
-                      tree_anc.has_value() ? reinterpret_cast<const unsigned*>(tree_anc->data_ptr<int>()) : nullptr, opt_ptr<float>(slopes));
+                      tree_anc.has_value() ? reinterpret_cast<const unsigned*>(tree_anc->data_ptr<int>()) : nullptr, opt_ptr<float>(slopes),
+                      opt_ptr<float>(log_rates), (int)keep_first, kv_stride);
     count(num_splits > 1 ? 2 : 1);
   } else {
     TORCH_CHECK(!tree_anc.has_value(), "tree masks need the tcgen05 attention (impl 0 / 2)");
@@ -973,7 +986,7 @@ TORCH_LIBRARY(sglb, m) {
   m.def("attn_fwd(Tensor q, Tensor k_cache, Tensor v_cache, Tensor(a!) out, Tensor(b!)? lse, Tensor(c!)? part_o, "
         "Tensor(d!)? part_lse, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, Tensor? tok2req, "
         "int max_q_len, int page_size, int num_splits, float scale, bool causal, int window, float logit_cap, "
-        "float k_scale, float v_scale, int impl, Tensor? tree_anc=None, Tensor? slopes=None) -> ()", &attn_fwd);
+        "float k_scale, float v_scale, int impl, Tensor? tree_anc=None, Tensor? slopes=None, Tensor? log_rates=None, int keep_first=0) -> ()", &attn_fwd);
   m.def("attn_decode_prof(Tensor buf) -> ()", &attn_decode_prof);
   m.def("green_ctx_streams(int device, int[] sm_counts) -> int[]", [](int64_t device, std::vector<int64_t> counts) {
     std::vector<long long> c(counts.begin(), counts.end());

@@ -33,12 +33,14 @@ bool attn_decode_tc_supported(int Hq, int Hkv, int D, int page_size);
 void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse, float* part_o, float* part_lse,
                     const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens, int B, int q_stride, int Hq, int Hkv,
                     int D, int num_slots, int page_size, int num_splits, float scale, int window, float logit_cap, int* sched, int num_sms,
-                    cudaStream_t stream, const float* slopes = nullptr);
+                    cudaStream_t stream, const float* slopes = nullptr, const float* log_rates = nullptr, int keep_first = 0,
+                    int kv_stride = 0);
 void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse, float* part_o,
                  float* part_lse, const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens,
                  const int* cu_q, int B, int T, int q_stride, int max_q_len, int Hq, int Hkv, int D, int num_slots,
                  int page_size, int num_splits, float scale, int causal, int window, float logit_cap, int* sched, int num_sms,
-                 cudaStream_t stream, const unsigned* tree_anc = nullptr, const float* slopes = nullptr);
+                 cudaStream_t stream, const unsigned* tree_anc = nullptr, const float* slopes = nullptr, const float* log_rates = nullptr,
+                 int keep_first = 0, int kv_stride = 0);
 
 // gemm_tc.cu
 void gemm_bf16_tc(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,

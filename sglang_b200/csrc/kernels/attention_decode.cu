@@ -56,7 +56,9 @@ struct DecodeParams {
   int pt_stride, Hq, Hkv, G, page_size, num_splits, B;
   float scale_log2, logit_cap;
   const float* slopes;      // optional [Hq]: distance bias, score -= slopes[h] * (seq_len - 1 - key position), applied after the cap
+  const float* log_rates;   // optional [Hq], with slopes: the bias is slopes[h] * ln(1 + log_rates[h] * distance) instead of linear (no cap)
   int window;
+  int keep_first;           // with a window: keys below this position stay visible (their tiles are walked first)
   int total_items;
   int* sched;             // [0] next item, [1] CTAs finished (the last one re-arms both)
   long long* prof;        // PROF builds: [ctas][32] per-role cycle accounting (tools/attn_decode_bench.py prof)
@@ -130,7 +132,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_O = tmem_base + 32;            // O^T: cols [32,48)
 
   // geometry of a work item: pure function of its id, evaluated identically by every role
-  struct Item { int b, kvh, split, seq_len, kv_hi, tile_begin, n_tiles; };
+  // key tiles are walked by a running index L: tiles of kept first tokens wholly before the window's first tile (tile L), then the window's (L + tile_skip)
+  struct Item {
+    int b, kvh, split, seq_len, kv_hi, tile_begin, n_tiles, keep_tiles, tile_skip;
+    __device__ __forceinline__ int tile(int j) const { const int L = tile_begin + j; return L < keep_tiles ? L : L + tile_skip; }
+  };
   auto decode_item = [&](int idx) {
     Item it;
     const int per_b = p.Hkv * p.num_splits;
@@ -141,9 +147,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     it.kv_hi = it.seq_len;
     int kv_lo = 0;
     if (p.window > 0) kv_lo = max(0, it.seq_len - p.window);
-    const int tile_lo = kv_lo / DA_KT, tile_hi = (it.kv_hi + DA_KT - 1) / DA_KT;
-    const int per_split = (tile_hi - tile_lo + p.num_splits - 1) / p.num_splits;
-    it.tile_begin = tile_lo + it.split * per_split;
+    const int tile_lo = kv_lo / DA_KT;
+    it.keep_tiles = min((p.keep_first + DA_KT - 1) / DA_KT, tile_lo);
+    it.tile_skip = tile_lo - it.keep_tiles;
+    const int tile_hi = (it.kv_hi + DA_KT - 1) / DA_KT - it.tile_skip;
+    const int per_split = (tile_hi + p.num_splits - 1) / p.num_splits;
+    it.tile_begin = it.split * per_split;
     it.n_tiles = max(0, min(tile_hi, it.tile_begin + per_split) - it.tile_begin);
     return it;
   };
@@ -180,7 +189,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int j = 0; j < it.n_tiles; ++j, ++g) {
         const int st = g % DA_STAGES;
         const uint32_t ph = (g / DA_STAGES) & 1;
-        const int key0 = (it.tile_begin + j) * DA_KT;
+        const int key0 = it.tile(j) * DA_KT;
         const int n_pages = min(pages_per_tile, (it.kv_hi - key0 + ps - 1) / ps);     // only pages that hold live keys
         const int pg0 = key0 / ps;
         const uint32_t bytes = (uint32_t)n_pages * ps * 256;
@@ -294,6 +303,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       float slope[GMAX];
 #pragma unroll
       for (int i = 0; i < GMAX; ++i) slope[i] = (HAS_CAP && p.slopes && i < G) ? p.slopes[it.kvh * G + i] : 0.f;
+      float rate[GMAX];
+#pragma unroll
+      for (int i = 0; i < GMAX; ++i) rate[i] = (HAS_CAP && p.log_rates && i < G) ? p.log_rates[it.kvh * G + i] : 0.f;
+      const bool log_bias = HAS_CAP && p.log_rates != nullptr;
       float m_run[GMAX], l_part[GMAX];
 #pragma unroll
       for (int i = 0; i < GMAX; ++i) { m_run[i] = -INFINITY; l_part[i] = 0.f; }
@@ -320,8 +333,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tmem_ld_wait();
         }
         if constexpr (PROF) { const long long t__ = clock64(); pacc[2] += t__ - tp__; tp__ = t__; }
-        const int key = (it.tile_begin + j) * DA_KT + row;
-        const bool live = key < it.kv_hi && key >= kv_first;
+        const int key = it.tile(j) * DA_KT + row;
+        const bool live = key < it.kv_hi && (key >= kv_first || key < p.keep_first);
+        const float dist = fmaxf((float)(it.seq_len - 1 - key), 0.f);
         float sv[GMAX], wmax[GMAX];
 #pragma unroll
         for (int i = 0; i < GMAX; ++i) {
@@ -329,7 +343,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (HAS_CAP) {
             float y = x * scale_nat;
             if (cap > 0.f) y = cap * tanhf(y * inv_cap);
-            x = (y - slope[i] * (float)(it.seq_len - 1 - key)) * inv_scale_nat;
+            const float bias = log_bias ? slope[i] * 0.6931471805599453f * __log2f(fmaf(rate[i], dist, 1.f)) : slope[i] * (float)(it.seq_len - 1 - key);
+            x = (y - bias) * inv_scale_nat;
           }
           sv[i] = live ? x * scale_log2 : -INFINITY;
           wmax[i] = warp_max(sv[i]);
@@ -476,7 +491,7 @@ void attn_decode_set_prof(long long* buf) { g_da_prof = buf; }
 void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse, float* part_o, float* part_lse,
                     const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens, int B, int q_stride, int Hq, int Hkv,
                     int D, int num_slots, int page_size, int num_splits, float scale, int window, float logit_cap, int* sched, int num_sms,
-                    cudaStream_t stream, const float* slopes) {
+                    cudaStream_t stream, const float* slopes, const float* log_rates, int keep_first, int kv_stride) {
   if (!attn_decode_tc_supported(Hq, Hkv, D, page_size)) throw std::runtime_error("sglb attn_decode_tc: unsupported shape");
   if (sched == nullptr) throw std::runtime_error("sglb attn_decode_tc: needs the work-queue counters");
   const int G = Hq / Hkv;
@@ -486,7 +501,9 @@ void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, voi
   uint32_t bq[4] = {64, (uint32_t)G, 1, 1};
   CUtensorMap tmQ = make_tmap(q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dq, sq, bq, CU_TENSOR_MAP_SWIZZLE_128B);
   uint64_t dk[3] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)num_slots};
-  uint64_t sk[2] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2};
+  if (kv_stride <= 0) kv_stride = Hkv * D;      // elements between two slots' rows
+  if (kv_stride < Hkv * D || (kv_stride % 8) != 0) throw std::runtime_error("sglb attn_decode_tc: cache rows must be 16-byte multiples at least Hkv * D wide");
+  uint64_t sk[2] = {(uint64_t)D * 2, (uint64_t)kv_stride * 2};
   uint32_t bk[3] = {64, 1, (uint32_t)page_size};
   CUtensorMap tmK = make_tmap(k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_128B);
   CUtensorMap tmV = make_tmap(v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -495,6 +512,8 @@ void attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, voi
   p.page_table = page_table; p.req_slots = req_slots; p.seq_lens = seq_lens;
   p.pt_stride = pt_stride; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.num_splits = num_splits; p.B = B;
   p.scale_log2 = scale * 1.4426950408889634f; p.logit_cap = logit_cap; p.window = window; p.slopes = slopes;
+  p.log_rates = slopes ? log_rates : nullptr; p.keep_first = window > 0 ? std::max(keep_first, 0) : 0;
+  if (p.log_rates && logit_cap > 0.f) throw std::runtime_error("sglb attn_decode_tc: the logarithmic distance bias takes no soft cap");
   p.total_items = B * Hkv * num_splits; p.sched = sched; p.prof = g_da_prof;
   const int ctas = std::min(p.total_items, num_sms);
   const bool capped = logit_cap > 0.f || slopes != nullptr;

@@ -46,6 +46,8 @@ struct AttnParams {
   int gx, gy, total_items;
   int* sched;         // [0] next item, [1] CTAs finished (the last one resets both: graph-replay safe)
   const float* slopes;        // optional [Hq]: distance bias, score -= slopes[h] * (query position - key position), applied after the cap
+  const float* log_rates;     // optional [Hq], with slopes: the bias is slopes[h] * ln(1 + log_rates[h] * distance) instead of linear (no cap)
+  int keep_first;             // with a window: keys below this position stay visible to every later query (their tiles are walked first)
   const unsigned* tree_anc;   // speculative tree verify: [T] bit k of tree_anc[t] = query token t may see draft key `prefix + k` (classic launch)
 };
 
@@ -71,10 +73,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int KV_TILE_BYTES = KT * ATT_D * 2;      // K or V tile
   constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;   // one 64-wide d-block of the tile
   constexpr int TMEM_COLS = (KT <= 64) ? 256 : 512;  // S0 | S1 | O(128)
-  const int tile_lo_all = kv_lo / KT;
-  const int tile_hi_all = (kv_hi + KT - 1) / KT;
-  const int per_split = (tile_hi_all - tile_lo_all + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = tile_lo_all + split * per_split;
+  // Key tiles are walked by a running index L: the tiles of the kept first tokens that lie wholly before the window's first tile come first
+  // (L < keep_tiles is tile L), then the window's tiles (tile L + tile_skip).  Without kept tokens keep_tiles = 0 and L counts from the window's first tile.
+  const int tile_lo_w = kv_lo / KT;
+  const int keep_tiles = min((p.keep_first + KT - 1) / KT, tile_lo_w);
+  const int tile_skip = tile_lo_w - keep_tiles;
+  const int tile_hi_all = (kv_hi + KT - 1) / KT - tile_skip;
+  const int per_split = (tile_hi_all + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = split * per_split;
   const int tile_end = min(tile_hi_all, tile_begin + per_split);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -147,7 +153,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      const int pg0 = (tile_begin + j) * pages_per_tile;
+      const int L = tile_begin + j;
+      const int pg0 = (L < keep_tiles ? L : L + tile_skip) * pages_per_tile;
       mbar_wait(&k_empty[st], ph ^ 1);
       mbar_expect_tx(&k_full[st], KV_TILE_BYTES);
       for (int i = 0; i < pages_per_tile; ++i) {
@@ -220,6 +227,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float cap = p.logit_cap, inv_cap = (HAS_CAP && p.logit_cap > 0.f) ? 1.f / p.logit_cap : 0.f;
     const float scale_nat = scale_log2 * 0.6931471805599453f, inv_scale_nat = 1.f / scale_nat;
     const float slope = (HAS_CAP && p.slopes) ? p.slopes[kvh * G + (r % G)] : 0.f;      // this row's head
+    const float rate = (HAS_CAP && p.log_rates) ? p.log_rates[kvh * G + (r % G)] : 0.f;
+    const float log_coef = slope * 0.6931471805599453f * inv_scale_nat;                 // ln(x) = ln 2 * lg2(x), in units of the raw score
     const int kv_last = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;
     const int kv_first = p.window > 0 ? q_pos - p.window + 1 : -(1 << 30);
 
@@ -235,12 +244,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int c = 0; c < NC; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sr[c]);
         tmem_ld_wait();
-        const int kv0 = (tile_begin + j) * KT;
+        const int Lj = tile_begin + j;
+        const int kv0 = (Lj < keep_tiles ? Lj : Lj + tile_skip) * KT;
         const bool need_mask = (kv0 + KT > kv_hi) || (p.causal && kv0 + KT - 1 > prefix + t0) ||
                                (p.window > 0 && kv0 < prefix + t_hi - p.window);
         // The inner loops are kept branch-free and tiny (the 128-wide body is fully unrolled: any per-element branch or
         // constant-bank reload multiplies into thousands of instructions and thrashes the instruction cache).
-        if (HAS_CAP) {   // soft-capping and / or distance bias (separate template instance): rewrite raw so raw*scale_log2 is the final logit
+        if (HAS_CAP && p.log_rates) {   // logarithmic distance bias: raw -= slope * ln(1 + rate * distance) / scale (one FFMA + MUFU.LG2 + FFMA more)
+          const float d0 = (float)(q_pos - kv0);
+#pragma unroll
+          for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float dist = fmaxf(d0 - (float)(c * 32 + i), 0.f);
+              sr[c][i] = __float_as_uint(fmaf(-log_coef, __log2f(fmaf(rate, dist, 1.f)), __uint_as_float(sr[c][i])));
+            }
+        } else if (HAS_CAP) {   // soft-capping and / or distance bias (separate template instance): rewrite raw so raw*scale_log2 is the final logit
           const float off = -slope * (float)(q_pos - kv0);      // bias of column 0; column c adds slope * c
 #pragma unroll
           for (int c = 0; c < NC; ++c)
@@ -254,13 +273,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float mx_raw = -INFINITY;
         if (need_mask) {
           const int hi = kv_last - kv0;     // columns > hi are masked   (per-thread: causal / sequence end)
-          const int lo = kv_first - kv0;    // columns < lo are masked   (sliding window)
+          const int lo = kv_first - kv0;    // columns < lo are masked   (sliding window) ...
+          const int kept = p.keep_first - kv0;   // ... unless they are kept first tokens (columns < kept)
 #pragma unroll
           for (int c = 0; c < NC; ++c) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int col = c * 32 + i;
-              const float v = (col > hi || col < lo) ? -INFINITY : __uint_as_float(sr[c][i]);
+              const float v = (col > hi || (col < lo && col >= kept)) ? -INFINITY : __uint_as_float(sr[c][i]);
               sr[c][i] = __float_as_uint(v);
               mx_raw = fmaxf(mx_raw, v);
             }
@@ -458,7 +478,10 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   const uint32_t tmem_O = tmem_base + 2 * KT;
 
   // geometry of one work item (identical code in every role: pure function of the item id)
-  struct Item { int b, kvh, split, t0, t_hi, q_start, q_len, seq_len, prefix, kv_hi, tile_begin, n_tiles; bool valid; };
+  struct Item {
+    int b, kvh, split, t0, t_hi, q_start, q_len, seq_len, prefix, kv_hi, tile_begin, n_tiles, keep_tiles, tile_skip; bool valid;
+    __device__ __forceinline__ int tile(int j) const { const int L = tile_begin + j; return L < keep_tiles ? L : L + tile_skip; }   // see the classic kernel
+  };
   auto decode_item = [&](int idx) {
     Item it;
     const int x = p.gx - 1 - (idx % p.gx);      // longest (latest) q tiles of a request first
@@ -475,9 +498,12 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     it.kv_hi = p.causal ? min(it.seq_len, it.prefix + it.t_hi) : it.seq_len;
     int kv_lo = 0;
     if (p.window > 0) kv_lo = max(0, it.prefix + it.t0 - p.window + 1);
-    const int tile_lo_all = kv_lo / KT, tile_hi_all = (it.kv_hi + KT - 1) / KT;
-    const int per_split = (tile_hi_all - tile_lo_all + p.num_splits - 1) / p.num_splits;
-    it.tile_begin = tile_lo_all + it.split * per_split;
+    const int tile_lo_w = kv_lo / KT;
+    it.keep_tiles = min((p.keep_first + KT - 1) / KT, tile_lo_w);
+    it.tile_skip = tile_lo_w - it.keep_tiles;
+    const int tile_hi_all = (it.kv_hi + KT - 1) / KT - it.tile_skip;
+    const int per_split = (tile_hi_all + p.num_splits - 1) / p.num_splits;
+    it.tile_begin = it.split * per_split;
     const int tile_end = min(tile_hi_all, it.tile_begin + per_split);
     it.n_tiles = it.valid ? max(0, tile_end - it.tile_begin) : 0;
     return it;
@@ -508,7 +534,7 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       for (int j = 0; j < it.n_tiles; ++j, ++g) {
         const int st = g & 1;
         const uint32_t ph = (g >> 1) & 1;
-        const int pg0 = (it.tile_begin + j) * pages_per_tile;
+        const int pg0 = it.tile(j) * pages_per_tile;
         SGLB_ATT_WAIT(&k_empty[st], ph ^ 1);
         mbar_expect_tx(&k_full[st], KV_TILE_BYTES);
         for (int i = 0; i < pages_per_tile; ++i) {
@@ -620,6 +646,8 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       if (lane == 0) SGLB_ATT_DBG(3, n_q, g);
       const int q_pos = it.prefix + tok;
       const float slope = (HAS_CAP && p.slopes) ? p.slopes[it.kvh * G + (r % G)] : 0.f;
+      const float rate = (HAS_CAP && p.log_rates) ? p.log_rates[it.kvh * G + (r % G)] : 0.f;
+      const float log_coef = slope * 0.6931471805599453f * inv_scale_nat;
       float m_i = -INFINITY, l_i = 0.f;
       const int kv_last = p.causal ? min(it.seq_len - 1, q_pos) : it.seq_len - 1;
       const int kv_first = p.window > 0 ? q_pos - p.window + 1 : -(1 << 30);
@@ -636,10 +664,19 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 #pragma unroll
           for (int c = 0; c < NC; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sr[c]);
           tmem_ld_wait();
-          const int kv0 = (it.tile_begin + j) * KT;
+          const int kv0 = it.tile(j) * KT;
           const bool need_mask = (kv0 + KT > it.kv_hi) || (p.causal && kv0 + KT - 1 > it.prefix + it.t0) ||
                                  (p.window > 0 && kv0 < it.prefix + it.t_hi - p.window);
-          if (HAS_CAP) {
+          if (HAS_CAP && p.log_rates) {
+            const float d0 = (float)(q_pos - kv0);
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float dist = fmaxf(d0 - (float)(c * 32 + i), 0.f);
+                sr[c][i] = __float_as_uint(fmaf(-log_coef, __log2f(fmaf(rate, dist, 1.f)), __uint_as_float(sr[c][i])));
+              }
+          } else if (HAS_CAP) {
             const float off = -slope * (float)(q_pos - kv0);
 #pragma unroll
             for (int c = 0; c < NC; ++c)
@@ -654,12 +691,13 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           if (need_mask) {
             const int hi = kv_last - kv0;
             const int lo = kv_first - kv0;
+            const int kept = p.keep_first - kv0;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const int col = c * 32 + i;
-                const float v = (col > hi || col < lo) ? -INFINITY : __uint_as_float(sr[c][i]);
+                const float v = (col > hi || (col < lo && col >= kept)) ? -INFINITY : __uint_as_float(sr[c][i]);
                 sr[c][i] = __float_as_uint(v);
                 mx_raw = fmaxf(mx_raw, v);
               }
@@ -813,7 +851,7 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
                  float* part_lse, const int* page_table, int pt_stride, const int* req_slots, const int* seq_lens,
                  const int* cu_q, int B, int T, int q_stride, int max_q_len, int Hq, int Hkv, int D, int num_slots, int page_size,
                  int num_splits, float scale, int causal, int window, float logit_cap, int* sched, int num_sms,
-                 cudaStream_t stream, const unsigned* tree_anc, const float* slopes) {
+                 cudaStream_t stream, const unsigned* tree_anc, const float* slopes, const float* log_rates, int keep_first, int kv_stride) {
   if (D != ATT_D) throw std::runtime_error("sglb attn_tc: head_dim must be 128");
   const int G = Hq / Hkv;
   if (G < 1 || G > 128 || (128 % G) != 0) throw std::runtime_error("sglb attn_tc: GQA group must divide 128");
@@ -825,7 +863,9 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
   uint32_t bq[4] = {64, (uint32_t)G, 1, (uint32_t)TQ};
   CUtensorMap tmQ = make_tmap(q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dq, sq, bq, CU_TENSOR_MAP_SWIZZLE_128B);
   uint64_t dk[3] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)num_slots};
-  uint64_t sk[2] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2};
+  if (kv_stride <= 0) kv_stride = Hkv * D;      // elements between two slots' rows (a layer may use the first Hkv * D columns of wider pool rows)
+  if (kv_stride < Hkv * D || (kv_stride % 8) != 0) throw std::runtime_error("sglb attn_tc: cache rows must be 16-byte multiples at least Hkv * D wide");
+  uint64_t sk[2] = {(uint64_t)D * 2, (uint64_t)kv_stride * 2};
   uint32_t bk[3] = {64, 1, (uint32_t)page_size};
   CUtensorMap tmK = make_tmap(k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_128B);
   CUtensorMap tmV = make_tmap(v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -835,6 +875,8 @@ void attn_fwd_tc(const void* q, const void* k_cache, const void* v_cache, void* 
   p.pt_stride = pt_stride; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.num_splits = num_splits; p.T = T;
   p.scale_log2 = scale * 1.4426950408889634f; p.logit_cap = logit_cap; p.causal = causal; p.window = window;
   p.tree_anc = tree_anc; p.slopes = slopes;
+  p.log_rates = slopes ? log_rates : nullptr; p.keep_first = window > 0 ? std::max(keep_first, 0) : 0;
+  if (p.log_rates && logit_cap > 0.f) throw std::runtime_error("sglb attn_tc: the logarithmic distance bias takes no soft cap");
   if (tree_anc != nullptr) {
     if (max_q_len > 32 || num_splits != 1 || window > 0) throw std::runtime_error("sglb attn_tc: tree masks cover <= 32 draft nodes, no split-KV / window");
     p.causal = 0;        // every draft key is a candidate; the ancestor bits decide

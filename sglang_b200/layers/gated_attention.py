@@ -12,9 +12,10 @@
 
 ``ops.attention_prepare`` does the second to fourth line and the cache write in one kernel; ``ops.window_attention`` the scores, mask,
 soft-max, value product and the gate (csrc/kernels/window_attention.cu), for prompt portions and decode tokens alike.  Scores, bias,
-soft-max, norms, angles and the gate are fp32; q and the cache are in the model dtype.  bf16 models with causal attention, no distance bias
-and key / value heads at most 128 wide run the framework's tcgen05 attention kernels (``ops.paged_attention``) on heads laid out 128
-columns wide (``pad``; see ``layers/window_attention.py``), followed by the gate.
+soft-max, norms, angles and the gate are fp32; q and the cache are in the model dtype.  bf16 models with key / value heads at most 128
+wide and a group size that divides 128 run the framework's tcgen05 attention kernels (``ops.paged_attention``: window, kept first tokens
+and the logarithmic bias are arguments of those kernels) on heads laid out 128 columns wide (``pad``; see ``layers/window_attention.py``),
+followed by the gate.
 
 The paged pool holds one flat row per token and plane (``FlatCacheSpec`` of ``layers/window_attention.py``); ``cache_idx`` selects the pool
 layer.  The window only masks: pages behind it stay with the request until it ends.
@@ -90,8 +91,7 @@ class GatedAttention(nn.Module):
     # ---- cache geometry
     def wants_padding(self, dtype) -> bool:
         """whether this layer would run the tcgen05 kernels if its pool rows are ``kv_heads * 128`` wide"""
-        return bool(self.tc_route and dtype == torch.bfloat16 and self.D <= 128 and self.Dv <= 128 and 128 % (self.H // self.G) == 0
-                    and self.window <= 0 and self.r1 is None)
+        return bool(self.tc_route and dtype == torch.bfloat16 and self.D <= 128 and self.Dv <= 128 and 128 % (self.H // self.G) == 0)
 
     @property
     def cache_width(self) -> int:
@@ -147,12 +147,13 @@ class GatedAttention(nn.Module):
         q = ops.attention_prepare(proj, H, G, D, Dv, fb.positions, kc, vc, fb.out_cache_loc, self.q_norm, self.k_norm, self.eps, self.inv_freq,
                                   v_first if self.value_mix else None, self.vmix, pad)
         gate = proj[:, self.rows - self.n_g:self.rows]
-        if pad == 128 and kc.shape[-1] == G * 128:
-            k4, v4 = kc.view(-1, G, 128), vc.view(-1, G, 128)
+        if self.tc_route and pad == 128 and kc.shape[-1] >= G * 128:
+            k4, v4 = kc[:, 0, :G * 128].unflatten(-1, (G, 128)), vc[:, 0, :G * 128].unflatten(-1, (G, 128))      # the leading columns of the pool's rows
             if ops.tc_attention_ok(q, k4, v4, fb.page_size):
                 dec = fb.cu_q is None
                 o = ops.paged_attention(q, k4, v4, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size, self.scale,
-                                        causal=True, window=-1, num_splits=fb.num_splits if dec else 1, workspace=fb.attn_workspace if dec else None)
+                                        causal=True, window=self.window, num_splits=fb.num_splits if dec else 1, workspace=fb.attn_workspace if dec else None,
+                                        slopes=self.r1, log_rates=self.r2, keep_first=self.keep_first)
                 return ops.sigmoid_gate(o, gate, Dv, self.out_scale, out)
         return ops.window_attention(q, kc, vc, G, Dv, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
                                     self.scale, 0.0, self.window, self.r1, None, D, pad, self.keep_first, self.r2, gate, self.out_scale,

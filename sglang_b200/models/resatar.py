@@ -214,13 +214,12 @@ class ResatarForCausalLM(nn.Module):
         bb.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype)
         bb.embed_tokens.weight.requires_grad_(False)
         bb.all_layers = nn.ModuleList([ResatarBlock(cfg, s, i, dtype) for i, s in enumerate(specs)])
-        # bf16 layers whose heads fit the tcgen05 kernels lay them out 128 columns wide, when that is also the pool's row width (the widest layer's)
+        # bf16 layers whose heads fit the tcgen05 kernels lay them out 128 columns wide in the leading columns of the pool's rows (the widest layer's width)
         attn = [b.attention() for b in bb.all_layers if b.attention() is not None]
-        widest = max([m.G * 128 if m.wants_padding(dtype) else m.cache_width for m in attn] or [0])
         for m in attn:
-            if m.wants_padding(dtype) and m.G * 128 == widest:
+            if m.wants_padding(dtype):
                 m.pad = 128
-        cache_width = max([m.cache_width for m in attn] or [0])
+        cache_width = -(-max([m.cache_width for m in attn] or [0]) // 8) * 8          # rows in multiples of 16 bytes (tensor maps over the pool)
         # per block: (index of its layer in the paged pool, index of its entry in the state pool); -1 where it has none
         self.slots_of: List[Tuple[int, int]] = []
         bb.layers, n_rec = [], 0           # ``layers``: what the runner sizes the paged pool from (one entry per attention layer)

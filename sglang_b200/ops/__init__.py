@@ -125,9 +125,10 @@ def attn_impl() -> int:
 def paged_attention(q, k_cache, v_cache, page_table, req_slots, seq_lens, cu_q, q_lens, max_q_len: int, page_size: int,
                     scale: float, causal: bool = True, window: int = -1, logit_cap: float = 0.0, k_scale: float = 1.0,
                     v_scale: float = 1.0, num_splits: int = 1, workspace=None, tok2req=None, out=None, lse=None,
-                    impl: Optional[int] = None, custom_mask=None, tree_anc=None, slopes=None):
+                    impl: Optional[int] = None, custom_mask=None, tree_anc=None, slopes=None, log_rates=None, keep_first: int = 0):
     """q [T,Hq,D]; caches [slots,Hkv,D]; cu_q None => decode (q_len 1).  ``slopes`` fp32 [Hq]: a distance bias ``- slopes[h] * (i - j)`` added to
-    the (capped) scores, on the tcgen05 kernels only (``tc_attention_ok`` says whether a call takes them).  ``tree_anc`` int32 [T]: speculative token-tree verification on the
+    the (capped) scores, or ``- slopes[h] * ln(1 + log_rates[h] * (i - j))`` when ``log_rates`` fp32 [Hq] is given; ``keep_first``: with a window,
+    keys at positions below it stay visible to every later query; all three on the tcgen05 kernels only (``tc_attention_ok`` says whether a call takes them).  ``tree_anc`` int32 [T]: speculative token-tree verification on the
     tcgen05 kernel (bit k = draft node k is an ancestor-or-self of this query node); ``custom_mask`` = the general (reference-path) form."""
     tree_ok = (tree_anc is not None and _use_native(q) and q.dtype == torch.bfloat16 and attn_impl() == 0 and q.shape[-1] == 128
                and k_cache.dtype == torch.bfloat16 and 128 % (q.shape[1] // k_cache.shape[1]) == 0 and int(max_q_len) <= 32 and window <= 0)
@@ -140,8 +141,8 @@ def paged_attention(q, k_cache, v_cache, page_table, req_slots, seq_lens, cu_q, 
         G = Hq // Hkv
         if impl == 0 and (D != 128 or k_cache.dtype != torch.bfloat16 or 128 % G != 0 or page_size < 8 or page_size > 128):
             impl = 1
-        if slopes is not None:
-            assert impl == 0 and tree_anc is None, "distance bias: tcgen05 attention kernels only"
+        if slopes is not None or keep_first > 0:
+            assert impl == 0 and tree_anc is None, "distance bias / kept first tokens: tcgen05 attention kernels only"
         part_o = part_lse = None
         if impl in (0, 2) and num_splits > 1:
             if workspace is None:
@@ -161,9 +162,10 @@ def paged_attention(q, k_cache, v_cache, page_table, req_slots, seq_lens, cu_q, 
             impl = 2        # same kernel family, persistent CTAs with an atomic work queue (falls back to the classic launch when small)
         torch.ops.sglb.attn_fwd(q, k_cache, v_cache, out, lse, part_o, part_lse, page_table, req_slots, seq_lens, cu_q, tok2req,
                                 int(max_q_len), int(page_size), int(num_splits), float(scale), bool(causal), int(window),
-                                float(logit_cap), float(k_scale), float(v_scale), int(impl), tree_anc if tree_ok else None, slopes)
+                                float(logit_cap), float(k_scale), float(v_scale), int(impl), tree_anc if tree_ok else None, slopes,
+                                log_rates if slopes is not None else None, int(keep_first) if window > 0 else 0)
         return out
-    assert slopes is None, "distance bias: tcgen05 attention kernels only"
+    assert slopes is None and keep_first <= 0, "distance bias / kept first tokens: tcgen05 attention kernels only"
     if custom_mask is None and tree_anc is not None:
         custom_mask = torch_ref.tree_anc_to_mask(tree_anc, q_lens, seq_lens)
     r = torch_ref.paged_attention(q, k_cache, v_cache, page_table, req_slots, seq_lens, q_lens, page_size, scale, causal,
@@ -179,12 +181,15 @@ def paged_attention(q, k_cache, v_cache, page_table, req_slots, seq_lens, cu_q, 
 
 
 def tc_attention_ok(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int) -> bool:
-    """whether ``paged_attention`` runs this call on the tcgen05 kernels: bf16, 128-wide heads, a group size that divides 128, contiguous caches"""
+    """whether ``paged_attention`` runs this call on the tcgen05 kernels: bf16, 128-wide heads, a group size that divides 128, caches whose rows are
+    contiguous (or the leading columns of wider rows that are multiples of 16 bytes)"""
     if not (_use_native(q) and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and attn_impl() == 0 and q.dim() == 3 and k_cache.dim() == 3):
         return False
     Hq, Hkv = q.shape[1], k_cache.shape[1]
     return (q.shape[-1] == 128 and k_cache.shape[-1] == 128 and v_cache.shape == k_cache.shape and Hq % Hkv == 0 and 128 % (Hq // Hkv) == 0
-            and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous() and q.is_contiguous())
+            and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0 and q.is_contiguous() and k_cache.stride() == v_cache.stride()
+            and k_cache.stride(2) == 1 and k_cache.stride(1) == 128 and k_cache.stride(0) >= Hkv * 128 and k_cache.stride(0) % 8 == 0
+            and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0)
 
 
 # ------------------------------------------------------------------ GEMM

@@ -229,8 +229,9 @@ def test_window_and_kept_token_edges_on_the_kernel():
 
 
 def test_tensor_core_route_of_gated_attention_against_the_general_kernel():
-    """bf16, heads padded to 128 columns: rotary causal attention with value blend and a per-head gate on the tcgen05 kernels and on the
-    general kernel give the same output (prompt portions and decode steps)"""
+    """bf16, heads padded to 128 columns: rotary causal attention with value blend and a per-head gate, and window attention with kept tokens,
+    the logarithmic bias, projection-wide norms, biases and an element gate, on the tcgen05 kernels and on the general kernel give the same
+    output (prompt portions and decode steps)"""
     _need()
     from types import SimpleNamespace
 
@@ -239,14 +240,21 @@ def test_tensor_core_route_of_gated_attention_against_the_general_kernel():
     dt = torch.bfloat16
     mix = GatedAttention(W, H, G, D, Dv, 0.1, 1e-5, dt, rotary=(80, scaled_inv_freq(80, 10000.0, None)), gate="head", value_mix=True).to(DEV)
     mix.vmix = 0.3
-    for p in (mix.in_weight, mix.o_weight):
-        p.data.copy_((torch.randn(p.shape, generator=g) * p.shape[1] ** -0.5).to(dt))
-    assert mix.wants_padding(dt)
-    mix.pad = 128
-    for q_lens, cached in (([130, 70], [0, 64]), ([1, 1], [200, 134])):
+    win = GatedAttention(W, H, G, D, Dv, 0.1, 1e-5, dt, bias=True, qk_norm=True, window=70, keep_first=3, log_bias=True, gate="element").to(DEV)
+    win.r1.data.copy_(torch.rand(H, generator=g) + 0.1)
+    win.r2.data.copy_(torch.rand(H, generator=g) * 2)
+    for m in (mix, win):
+        for p in (m.in_weight, m.o_weight):
+            p.data.copy_((torch.randn(p.shape, generator=g) * p.shape[1] ** -0.5).to(dt))
+        for p in (m.q_norm, m.k_norm, m.in_bias, m.o_bias):
+            if p is not None:
+                p.data.copy_((torch.rand(p.shape, generator=g) + 0.5).to(dt))
+        assert m.wants_padding(dt)
+        m.pad = 128
+    for mix, q_lens, cached in ((mix, [130, 70], [0, 64]), (mix, [1, 1], [200, 134]), (win, [130, 70], [0, 64]), (win, [1, 1], [200, 134])):
         cu, seq = _ragged(q_lens, cached)
         T = sum(q_lens)
-        pt, kc, vc = _paged(2, 260, ps, G * 128, dt, g)
+        pt, kc, vc = _paged(2, 260, ps, G * 128 + (72 if mix is win else 0), dt, g)       # also as the leading columns of wider pool rows
         pos = torch.cat([torch.arange(c, c + q) for c, q in zip(cached, q_lens)]).int()
         req = torch.cat([torch.full((q,), s) for s, q in zip([1, 2], q_lens)])
         loc = (pt[req.long(), (pos // ps).long()] * ps + pos % ps).int()
@@ -262,11 +270,82 @@ def test_tensor_core_route_of_gated_attention_against_the_general_kernel():
             GatedAttention.tc_route = route
             try:
                 if route:
-                    assert ops.tc_attention_ok(torch.empty(T, H, 128, dtype=dt, device=DEV), pool.k(0).view(-1, G, 128), pool.v(0).view(-1, G, 128), ps)
+                    assert ops.tc_attention_ok(torch.empty(T, H, 128, dtype=dt, device=DEV), pool.k(0)[:, 0, :G * 128].unflatten(-1, (G, 128)),
+                                               pool.v(0)[:, 0, :G * 128].unflatten(-1, (G, 128)), ps)
                 outs.append(mix.forward(h, fb, 0, vf).float().cpu())
             finally:
                 GatedAttention.tc_route = True
         torch.testing.assert_close(outs[0], outs[1], rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("window,keep", [(100, 4), (300, 130), (64, 0), (1, 2), (500, 1), (129, 128), (-1, 3)])
+@pytest.mark.parametrize("G,rep,ps", [(1, 8, 16), (2, 4, 64), (3, 1, 32), (1, 16, 128)])
+def test_tensor_core_attention_with_window_kept_tokens_and_log_bias(window, keep, G, rep, ps, monkeypatch):
+    """``paged_attention`` on the tcgen05 kernels (classic and persistent prompt kernels, decode kernel with one and several key splits)
+    against the fp32 reference: windows that start inside a key tile, kept tokens inside the first tile, filling it and reaching into the
+    second, requests shorter than the window, ragged portions beside single tokens"""
+    _need()
+    from sglang_b200.environ import envs
+
+    g = torch.Generator().manual_seed(11)
+    H, D, dt = G * rep, 128, torch.bfloat16
+    q_lens, cached = [300, 1, 2, 200, 70], [150, 600, 0, 0, 513]
+    cu, seq = _ragged(q_lens, cached)
+    T = sum(q_lens)
+    pt, kc, vc = _paged(5, max(seq), ps, G * D, dt, g)
+    slots = [1, 2, 3, 4, 5]
+    q = torch.randn(T, H, D, generator=g).to(dt)
+    r1, r2 = torch.rand(H, generator=g) + 0.1, torch.rand(H, generator=g) * 2
+    scale = 0.12
+    k3, v3 = kc.to(DEV).view(-1, G, D), vc.to(DEV).view(-1, G, D)
+    assert ops.tc_attention_ok(q.to(DEV), k3, v3, ps)
+    ref = torch_ref.window_attention(q, kc, vc, G, D, pt, _i32(slots, "cpu"), _i32(seq, "cpu"), _i32(q_lens, "cpu"), ps, scale, 0.0, window, r1, None, 0, 0, keep, r2)
+    for persist in ("1", "0"):
+        monkeypatch.setenv(envs.SGLB_ATTN_PERSIST.name, persist)
+        got = ops.paged_attention(q.to(DEV), k3, v3, pt.to(DEV), _i32(slots), _i32(seq), _i32(cu), _i32(q_lens), max(q_lens), ps, scale, causal=True,
+                                  window=window, slopes=r1.to(DEV), log_rates=r2.to(DEV), keep_first=keep)
+        torch.testing.assert_close(got.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+    # without a bias: the kept tokens and the window alone (the instance of the kernels without score rewriting)
+    ref0 = torch_ref.window_attention(q, kc, vc, G, D, pt, _i32(slots, "cpu"), _i32(seq, "cpu"), _i32(q_lens, "cpu"), ps, scale, 0.0, window, None, None, 0, 0, keep)
+    got0 = ops.paged_attention(q.to(DEV), k3, v3, pt.to(DEV), _i32(slots), _i32(seq), _i32(cu), _i32(q_lens), max(q_lens), ps, scale, causal=True,
+                               window=window, keep_first=keep)
+    torch.testing.assert_close(got0.cpu().float(), ref0, rtol=2e-2, atol=2e-2)
+    # decode: the last token of every request alone
+    last = torch.tensor([c - 1 for c in cu[1:]])
+    qd = q[last].contiguous()
+    refd = torch_ref.window_attention(qd, kc, vc, G, D, pt, _i32(slots, "cpu"), _i32(seq, "cpu"), None, ps, scale, 0.0, window, r1, None, 0, 0, keep, r2)
+    for splits in (1, 3):
+        gotd = ops.paged_attention(qd.to(DEV), k3, v3, pt.to(DEV), _i32(slots), _i32(seq), None, None, 1, ps, scale, causal=True, window=window,
+                                   num_splits=splits, slopes=r1.to(DEV), log_rates=r2.to(DEV), keep_first=keep)
+        torch.testing.assert_close(gotd.cpu().float(), refd, rtol=2e-2, atol=2e-2)
+
+
+def test_window_and_kept_token_edges_on_the_tensor_core_kernels():
+    """the standout value of the edge test above, on the tcgen05 kernels: seen or not to the token at the window's far edge, at the last kept
+    position and at the first position behind the kept ones, with the mark inside the first key tile, at its end and in the second"""
+    _need()
+    H, G, D, ps, dt = 2, 1, 128, 16, torch.bfloat16
+    g = torch.Generator().manual_seed(12)
+    for W, keep in ((68, 5), (200, 128), (150, 131)):
+        for mark, seen_at, hidden_at in ((keep + 35, keep + 35 + W - 1, keep + 35 + W), (keep - 1, 700, None), (keep, keep + W - 1, keep + W), (300, 300 + W - 1, 300 + W)):
+            pt, kc, vc = _paged(1, 720, ps, D, dt, g)
+            kc, vc = kc * 0.1, vc * 0.1
+            s = int(pt[1, mark // ps]) * ps + mark % ps
+            kc[s, 0] = 0.0
+            kc[s, 0, 0] = 6.0
+            vc[s, 0] = 50.0
+            k3, v3 = kc.to(DEV).view(-1, G, D), vc.to(DEV).view(-1, G, D)
+            for qpos in [p for p in (seen_at, hidden_at) if p is not None]:
+                q = torch.zeros(1, H, D)
+                q[0, :, 0] = 3.0
+                for n_q in (1, 5, 140):                         # decode step / the last query of a short and of a two-tile portion
+                    if n_q > qpos + 1:
+                        continue
+                    qq = torch.cat([torch.zeros(n_q - 1, H, D), q]).to(dt).to(DEV)
+                    out = ops.paged_attention(qq, k3, v3, pt.to(DEV), _i32([1]), _i32([qpos + 1]), _i32([0, n_q]) if n_q > 1 else None,
+                                              _i32([n_q]) if n_q > 1 else None, n_q, ps, 1.0, causal=True, window=W, slopes=torch.full((H,), 0.1, device=DEV),
+                                              log_rates=torch.full((H,), 0.5, device=DEV), keep_first=keep)
+                    assert (float(out[-1, 0, 0]) > 5.0) == (qpos == seen_at), (W, keep, mark, qpos, n_q)
 
 
 def test_router_and_ungated_shared_combine():
