@@ -7,9 +7,9 @@ Two parts, random weights, one GPU:
    ``*M*M``; its feed-forward width is chosen so that a token runs as many feed-forward columns as a Resatar token: ``top * expert ff + shared
    ff``), both through ``Scheduler.replay_step`` (the serving step).
 2. **kernels**: each new kernel beside the like op of the closest model on the same shapes: the ragged selective scan vs the chunked PyTorch
-   scan Jamba prompts run and vs the tensor expressions of its decode step; the general attention kernel with kept tokens, logarithmic bias
-   and gate epilogue vs the tcgen05 paged attention kernel with the same window; rotary gated attention on the tcgen05 kernels (+ gate) vs the
-   same kernels alone; ``attention_prepare`` vs ``rope_kv_write``; the constant-decay scan vs the Mamba-2 scan it shares a kernel with; the
+   scan Jamba prompts run and vs the tensor expressions of its decode step; window attention with kept tokens, logarithmic bias and an
+   element gate, on the tcgen05 kernels (bf16 serving) and on the general kernel (fp32 serving), vs the tcgen05 paged attention kernel with the
+   same window alone; rotary gated attention on the tcgen05 kernels (+ gate) vs the same kernels alone; ``attention_prepare`` vs ``rope_kv_write``; the constant-decay scan vs the Mamba-2 scan it shares a kernel with; the
    scalar sandwich norm vs the vector one; the gated norm vs the plain one; the element-wise activation vs ``silu_and_mul``.
    Roofline: algorithmic bytes over the measured copy bandwidth; for prompt attention also FLOPs over the measured bf16 GEMM rate.
 
