@@ -37,7 +37,7 @@ class ExpertDistributionRecorder:
         self.num_passes = 0
         self.enabled = False
 
-    # kept for callers that used the round-1 attribute
+    # kept for callers that used the earlier attribute
     @property
     def counts(self) -> np.ndarray:
         return self.dev_counts.cpu().numpy().copy()

@@ -85,7 +85,7 @@ def test_tcp_transport_rejects_pickles_and_wrong_secret(monkeypatch):
             return (exec, ("raise SystemExit('pickle executed')",))
 
     blob = pickle.dumps(Boom())
-    with socket.create_connection(("127.0.0.1", rx.port), timeout=5) as c:       # the round-1 frame: u64 length + pickle
+    with socket.create_connection(("127.0.0.1", rx.port), timeout=5) as c:       # the plain frame: u64 length + pickle
         c.sendall(struct.pack("<Q", len(blob)) + blob)
         c.settimeout(2)
         try:
