@@ -1,5 +1,5 @@
 """A plain, slow restatement of the Resatar decoder, written from its equations with one function per mechanism.  It shares no code with the
-serving path: every token is visited one by one, every sum is spelled out, everything is float64.  The tests compare the engine with it.
+serving path: every token is visited one by one, every sum is spelled out, everything is float64 but the rotary angle (see ``rotate``).  The tests compare the engine with it.
 
 Notation: ``h`` the normed input of a sublayer, ``p`` a position (from 0), ``W x`` a stored [out, in] matrix applied to a vector.
 """
@@ -56,11 +56,13 @@ def rotary_frequencies(rot):
 
 
 def rotate(x, p, freqs, dims):
-    """x [heads, dim] at position p: coordinate i pairs with i + dims/2 inside the first ``dims`` coordinates of every head"""
+    """x [heads, dim] at position p: coordinate i pairs with i + dims/2 inside the first ``dims`` coordinates of every head.  The design
+    keeps frequencies and angles in 32-bit floats, so the angle is the rounded product of the rounded frequency: at position 1000 that
+    rounding moves an angle by up to 3e-5, which a float64 angle would count as an error of the engine"""
     y = x.clone()
     half = dims // 2
     for i in range(half):
-        a = p * freqs[i]
+        a = float(torch.tensor(float(p), dtype=torch.float32) * torch.tensor(freqs[i], dtype=torch.float32))
         c, s = math.cos(a), math.sin(a)
         u, v = x[:, i], x[:, i + half]
         y[:, i] = u * c - v * s
