@@ -166,7 +166,7 @@ def run_reference(args) -> None:
     modes = [m for m in os.environ.get("SGLB_REF_MODES", "stock,fi,fi_nopg,degraded,degraded_nopg").split(",") if m]
     fails = []
     budget = 900.0 + 60.0 * (args.steps + args.warmup)
-    deadline = time.time() + 2.0 * budget          # the whole ladder: a box where every mode hangs must not eat the round
+    deadline = time.time() + 2.0 * budget          # the whole ladder: a box where every mode hangs must still end in bounded time
     for m in modes:
         left = deadline - time.time()
         if left < 120.0:
