@@ -206,7 +206,13 @@ def test_multi_tokenizer_workers_share_one_scheduler(tmp_path, frontend):
                 time.sleep(0.5)
         else:
             pytest.fail("server did not come up")
-        time.sleep(1.0)                                   # let the second worker finish binding
+        seen, t_end = set(), time.time() + 60.0           # the second worker binds a little later: wait until both have answered
+        while len(seen) < 2 and time.time() < t_end:
+            try:
+                seen.add(urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1).headers.get("x-sglb-worker"))
+            except Exception:
+                pass
+            time.sleep(0.05)
         ref = sgl.Engine(model_path="dummy:tiny-llama", page_size=4, log_level="error")
         prompts = [f"prompt number {i} about things" for i in range(24)]
         sp = {"max_new_tokens": 6, "temperature": 0, "ignore_eos": True}
