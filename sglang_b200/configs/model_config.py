@@ -421,8 +421,26 @@ def resatar_config(hf: Dict[str, Any]) -> Dict[str, Any]:
                 hybrid={"layers": layers})
 
 
+def rumuvik_config(hf: Dict[str, Any]) -> Dict[str, Any]:
+    """Rumuvik ``config.json`` -> ModelConfig fields.  ``layers[i]`` = ``type`` of the mixer (``attention`` | ``latent_attention`` | ``mlstm``), its
+    sizes and constants under ``mixer``, the feed-forward under ``mlp`` (``kind`` ``dense``) or null; ``loop`` = ``{start, stop, times}``;
+    ``embedding`` = ``{scale}``; globals ``width``, ``vocab``, ``norm.eps``.  The flat fields are summaries for code that sizes buffers; the
+    model reads ``hybrid``."""
+    layers = [dict(l) for l in hf["layers"]]
+    width = int(hf["width"])
+    ffs = [int(l["mlp"]["ff"]) for l in layers if l.get("mlp")]
+    heads = max([int(l["mixer"]["heads"]) for l in layers] or [1])
+    return dict(architecture="Rumuvik", hidden_size=width, vocab_size=int(hf["vocab"]), num_hidden_layers=len(layers),
+                rms_norm_eps=float((hf.get("norm") or {}).get("eps", 1e-6)), final_logit_softcapping=0.0,
+                num_attention_heads=heads, num_key_value_heads=1, head_dim=max([int(l["mixer"]["dim"]) for l in layers] or [width // heads]),
+                intermediate_size=max(ffs or [width]), num_local_experts=0, num_experts_per_tok=0,
+                max_position_embeddings=int(hf.get("max_positions") or (1 << 20)), tie_word_embeddings=False, eos_token_id=None,
+                dtype={"float16": "float16", "float32": "float32"}.get(hf.get("dtype") or "bfloat16", "bfloat16"),
+                hybrid={"layers": layers, "loop": hf.get("loop") or None, "embedding": hf.get("embedding") or {}})
+
+
 # configurations that list their layers one by one, chosen by the file's ``architecture`` key
-_LAYER_LIST_READERS = {"Rirotar": rirotar_config, "Zaparax": zaparax_config, "Resatar": resatar_config}
+_LAYER_LIST_READERS = {"Rirotar": rirotar_config, "Zaparax": zaparax_config, "Resatar": resatar_config, "Rumuvik": rumuvik_config}
 
 
 def _has_native_class(arch: str) -> bool:

@@ -19,10 +19,16 @@ through the log-sum-exp (``o * sigmoid(lse - sink)``).  Per (query, key, head) t
 instead of ``2 * kv_rank`` on CUDA cores.  Decode, fp32 serving and every other head size stay on the absorbed kernel.
 
 The window only masks: pages of tokens that left the window are still held until the request ends (the pool is sized by live tokens).
+
+``RotaryLatentAttention`` is the positional form: queries pass a normed latent of their own, every head has ``dim`` unrotated and
+``rot_dim`` rotary query / key coordinates, and ONE rotary key part per token is shared by all heads.  The cache row is
+``[c (kv_rank) | rotary key (rot_dim)]``; in the absorbed form the query is ``[W_uk,h^T q_h | rotary part]`` and the same kernel scores over
+the whole row while only its first ``kv_rank`` columns are values (``ops.latent_attention(v_rank=...)``).
 """
 from __future__ import annotations
 
-from typing import Optional
+import math
+from typing import Optional, Tuple
 
 import numpy as np
 import torch
@@ -145,4 +151,94 @@ class WindowedLatentAttention(nn.Module):
         o_lat = ops.latent_attention(q_lat, cache, self.R, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
                                      self.attn.scale, self.attn.window, self.sinks, fb.max_kv_len)
         o = torch.bmm(o_lat.transpose(0, 1), uv).transpose(0, 1).reshape(T, self.H * self.Dv)
+        return ops.linear(o.to(h.dtype), self.o_weight)
+
+
+def yarn_inv_freq(dims: int, base: float, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, float]:
+    """rotary frequencies ``f_i = base^(-2i/dims)``, i < dims/2, with YaRN's blend, and the factor on sine and cosine.
+
+    ``scaling = {factor, original, fast, slow}``: with ``dim(t) = dims ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(dim(fast)), 0)``,
+    ``hi = min(ceil(dim(slow)), dims - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency is
+    ``f_i / factor * ramp_i + f_i (1 - ramp_i)``, and sine and cosine are multiplied by ``0.1 ln(factor) + 1``.  Without ``scaling``:
+    the plain frequencies and 1."""
+    f = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    mult = 1.0
+    if scaling:
+        factor, orig, fast, slow = float(scaling["factor"]), float(scaling["original"]), float(scaling["fast"]), float(scaling["slow"])
+        dim_of = lambda t: dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(float(base)))
+        lo, hi = max(math.floor(dim_of(fast)), 0), min(math.ceil(dim_of(slow)), dims - 1)
+        ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(dims // 2)]
+        f = [fi / factor * r + fi * (1.0 - r) for fi, r in zip(f, ramp)]
+        mult = 0.1 * math.log(factor) + 1.0
+    return torch.tensor(f, dtype=torch.float64).float(), mult
+
+
+class RotaryLatentAttention(nn.Module):
+    """latent attention with a query latent and a decoupled rotary part (neighbouring coordinates paired), causal, ordinary soft-max:
+
+        c_q = rmsnorm(W_dq h) * w_q,   q_h = W_uq,h c_q = [q_h^0 (dim) | q_h^r (rot_dim)]
+        [c' | k^r] = W_dkv h,          c = rmsnorm(c') * w_kv  (kv_rank),   k^r (rot_dim) shared by all heads
+        s_hij = scale * (q_hi^0 . W_uk,h c_j + rot_i(q_hi^r) . rot_j(k_j^r)),   o_hi = W_uv,h sum_j softmax_j(s_hij) c_j
+
+    ``cache`` is a [slots, 1, >= kv_rank + rot_dim] plane of the paged pool that the model hands in (a latent layer needs one plane)."""
+
+    def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, scale: Optional[float], eps: float, dtype,
+                 rotary: Optional[Tuple[torch.Tensor, float]] = None, window: int = -1):
+        super().__init__()
+        self.H, self.D, self.Dr, self.Dv, self.R, self.Rq = heads, dim, rot_dim, vdim, kv_rank, q_rank
+        self.eps, self.window = eps, int(window or -1)
+        self.scale = float(scale) if scale is not None else (dim + rot_dim) ** -0.5
+        mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype), requires_grad=False)
+        self.down_weight = mk(q_rank + kv_rank + rot_dim, width)       # rows [query latent | key/value latent | rotary key]: one GEMM
+        self.q_norm = nn.Parameter(torch.ones(q_rank, dtype=dtype), requires_grad=False)
+        self.kv_norm = nn.Parameter(torch.ones(kv_rank, dtype=dtype), requires_grad=False)
+        self.uq = mk(heads * (dim + rot_dim), q_rank)
+        self.uk = mk(heads * dim, kv_rank)
+        self.uv = mk(heads * vdim, kv_rank)
+        self.o_weight = mk(width, heads * vdim)
+        assert rot_dim % 2 == 0 and (rotary is None or rotary[0].numel() == rot_dim // 2)
+        self.inv_freq = nn.Parameter(rotary[0].float().clone(), requires_grad=False) if rotary is not None and rot_dim else None
+        self.rot_mult = float(rotary[1]) if rotary is not None else 1.0
+        self._uk32 = self._uv32 = None
+
+    @property
+    def cache_width(self) -> int:
+        return self.R + self.Dr
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        if leaf == "dq":
+            self.down_weight.data[:self.Rq].copy_(w)
+        elif leaf == "dkv":
+            self.down_weight.data[self.Rq:].copy_(w)
+        elif leaf == "dq.norm":
+            self.q_norm.data.copy_(w)
+        elif leaf == "dkv.norm":
+            self.kv_norm.data.copy_(w)
+        elif leaf in ("uq", "uk", "uv"):
+            getattr(self, leaf).data.copy_(w)
+            self._uk32 = self._uv32 = None
+        elif leaf == "o":
+            self.o_weight.data.copy_(w)
+        else:
+            return False
+        return True
+
+    def _absorbed(self):
+        if self._uk32 is None or self._uk32.device != self.uk.device:
+            self._uk32 = self.uk.detach().float().view(self.H, self.D, self.R).contiguous()                   # [H, D, R]
+            self._uv32 = self.uv.detach().float().view(self.H, self.Dv, self.R).transpose(1, 2).contiguous()  # [H, R, Dv]
+        return self._uk32, self._uv32
+
+    def forward(self, h: torch.Tensor, fb: ForwardBatch, cache: torch.Tensor) -> torch.Tensor:
+        T, H, D, Dr, R = h.shape[0], self.H, self.D, self.Dr, self.R
+        down = ops.linear(h, self.down_weight)
+        cq = ops.latent_prepare(down, self.Rq, self.q_norm, R, Dr, self.kv_norm, self.eps, fb.positions, self.inv_freq, self.rot_mult, cache,
+                                fb.out_cache_loc)
+        q = ops.linear(cq, self.uq).view(T, H, D + Dr)
+        uk, uv = self._absorbed()
+        q_abs = torch.bmm(q[:, :, :D].float().transpose(0, 1), uk)                                            # [H, T, R] fp32
+        q_lat = ops.latent_query(q, q_abs, D, Dr, fb.positions, self.inv_freq, self.rot_mult)                 # [T, H, R + Dr] fp32
+        o_lat = ops.latent_attention(q_lat, cache, R + Dr, fb.page_table, fb.req_slots, fb.seq_lens, fb.cu_q, fb.q_lens, fb.max_q_len, fb.page_size,
+                                     self.scale, self.window, None, fb.max_kv_len, v_rank=R)
+        o = torch.bmm(o_lat.transpose(0, 1), uv).transpose(0, 1).reshape(T, H * self.Dv)
         return ops.linear(o.to(h.dtype), self.o_weight)

@@ -190,18 +190,21 @@ class LayeredStatePool:
     inputs of the short convolution, model dtype) and ``ssm[i]`` [slots, heads_i, key_dim_i, value_dim_i] (fp32 matrix state), both indexed
     by the request slot like the page table.  The two lists index like ``MambaPool``'s stacked tensors (``pool.conv[layer]``), so a mixer
     written against one works against the other.  A slot needs no clearing on reuse: the kernels start a request whose cached length is
-    zero from a zero state and zero convolution history."""
+    zero from a zero state and zero convolution history.  ``aux[i]`` [slots, n_i] holds a layer's further fp32 numbers per request (e.g. the
+    running maximum of exponential gates), where its geometry asks for some."""
 
     def __init__(self, slots: int, geometry, dtype: torch.dtype, device, token_history: bool = False):
-        """geometry: one ``(conv_channels, taps, heads, key_dim, value_dim)`` per recurrent layer.  ``token_history``: also keep every
-        request's last token id (``tokens`` int32 [slots]) for embeddings that look one token back (``ops.bigram_embedding``)."""
+        """geometry: one ``(conv_channels, taps, heads, key_dim, value_dim)`` or ``(..., value_dim, aux)`` per recurrent layer.
+        ``token_history``: also keep every request's last token id (``tokens`` int32 [slots]) for embeddings that look one token back
+        (``ops.bigram_embedding``)."""
         self.slots = slots
-        self.conv = [torch.zeros(slots, c, max(1, k - 1), dtype=dtype, device=device) for c, k, _, _, _ in geometry]
-        self.ssm = [torch.zeros(slots, h, dk, dv, dtype=torch.float32, device=device) for _, _, h, dk, dv in geometry]
+        self.conv = [torch.zeros(slots, g[0], max(1, g[1] - 1), dtype=dtype, device=device) for g in geometry]
+        self.ssm = [torch.zeros(slots, g[2], g[3], g[4], dtype=torch.float32, device=device) for g in geometry]
+        self.aux = [torch.zeros(slots, g[5] if len(g) > 5 else 0, dtype=torch.float32, device=device) for g in geometry]
         self.tokens = torch.zeros(slots, dtype=torch.int32, device=device) if token_history else None
 
     def _all(self):
-        return self.conv + self.ssm + ([self.tokens] if self.tokens is not None else [])
+        return self.conv + self.ssm + self.aux + ([self.tokens] if self.tokens is not None else [])
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._all())

@@ -151,6 +151,9 @@ def _register_builtins() -> None:
     from . import resatar as _rs
 
     register_model("Resatar", _rs.ResatarForCausalLM)
+    from . import rumuvik as _rv
+
+    register_model("Rumuvik", _rv.RumuvikForCausalLM)
     from . import transformers_fallback as _tff
 
     register_model("TransformersForCausalLM", _tff.TransformersForCausalLM)

@@ -56,6 +56,15 @@ def layer_runs(n_layers: int, loop: Optional[dict]) -> List[int]:
     return list(range(a)) + list(range(a, b)) * times + list(range(b, n_layers))
 
 
+def layer_passes(n_layers: int, loop: Optional[dict]) -> List[Tuple[int, bool]]:
+    """``layer_runs`` with a mark on every run that opens a pass of the loop after the first (where a design adds something between passes)"""
+    order = layer_runs(n_layers, loop)
+    if not loop or len(order) == n_layers:
+        return [(i, False) for i in order]
+    a, b = int(loop.get("start", 0)), int(loop.get("stop", 0))
+    return [(i, a <= r < a + (b - a) * int(loop.get("times", 1)) and r > a and (r - a) % (b - a) == 0) for r, i in enumerate(order)]
+
+
 class SiluGLU(nn.Module):
     def __init__(self, width: int, ff: int, dtype):
         super().__init__()

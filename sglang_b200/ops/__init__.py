@@ -487,18 +487,20 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.T
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_table: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
                      cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], max_q_len: int, page_size: int, scale: float, window: int = -1,
-                     sinks: Optional[torch.Tensor] = None, max_kv_len: int = 0) -> torch.Tensor:
+                     sinks: Optional[torch.Tensor] = None, max_kv_len: int = 0, v_rank: Optional[int] = None) -> torch.Tensor:
     """absorbed multi-query attention over a paged cache of latent rows with a sliding window and per-head sinks
     (csrc/kernels/latent_attention.cu; contract in ``torch_ref.latent_attention``).  ``cu_q`` None = one query per request.
-    ``max_kv_len`` (host-side longest sequence; 0 = unknown) only steers how decode splits the keys over CTAs."""
+    ``max_kv_len`` (host-side longest sequence; 0 = unknown) only steers how decode splits the keys over CTAs.  ``v_rank``: how many leading
+    columns of a cached row are its value (default: all ``rank``; the others, e.g. a rotary key part, take part in the scores only)."""
+    v_rank = int(rank if v_rank is None else v_rank)
     if (_use_native(q_lat) and q_lat.dtype == torch.float32 and cache.dtype in (torch.bfloat16, torch.float32) and q_lat.is_contiguous()
             and rank <= 1024 and req_slots.numel() <= 65535):          # (a key tile and one head's accumulators have to fit shared memory)
-        out = torch.empty_like(q_lat)
+        out = torch.empty(q_lat.shape[0], q_lat.shape[1], v_rank, dtype=torch.float32, device=q_lat.device)
         torch.ops.sglb.latent_attention(q_lat, cache, int(rank), page_table, req_slots, seq_lens, cu_q, int(max_q_len),
                                         int(max_kv_len) if max_kv_len else (int(window) if window > 0 else 4096), int(page_size), float(scale),
-                                        int(window), sinks, out)
+                                        int(window), sinks, out, v_rank)
         return out
-    return torch_ref.latent_attention(q_lat, cache, rank, page_table, req_slots, seq_lens, q_lens, page_size, scale, window, sinks)
+    return torch_ref.latent_attention(q_lat, cache, rank, page_table, req_slots, seq_lens, q_lens, page_size, scale, window, sinks, v_rank)
 
 
 def _delta_shape_ok(Dk: int, Dv: int) -> bool:
@@ -571,22 +573,27 @@ def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: flo
 def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
                 A_log: Optional[torch.Tensor], D: Optional[torch.Tensor], state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
                 cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor], H: int, P: int, N: int, G: int,
-                decay: Optional[torch.Tensor] = None) -> torch.Tensor:
+                decay: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Mamba-2 recurrence over a ragged batch (prompt portions and single decode tokens alike): softplus step size, decay, the fp32 state update
     and read-out, the skip term and the silu(z) gate in one kernel (csrc/kernels/mamba.cu; semantics in ``torch_ref.mamba2_scan``).  ``z`` and
     ``dt_raw`` may be column views of the projection's output.  ``decay`` fp32 [H] replaces the input-dependent step: step size 1, the
-    head's state times its constant every token (``dt_raw``, ``dt_bias``, ``A_log`` unused)."""
+    head's state times its constant every token (``dt_raw``, ``dt_bias``, ``A_log`` unused).  ``gates`` fp32 [T, H, n >= 2] contiguous: every
+    token brings its decay ``gates[t, h, 0]`` and its step ``gates[t, h, 1]`` (exponentially gated memories such as ``layers/mlstm.py``)."""
+    fixed = decay is not None or gates is not None
     if (_use_native(u) and u.dtype == torch.float32 and u.is_contiguous() and state.dtype == torch.float32 and N <= 1024 and req_slots.numel() <= 65535
-            and (decay is not None or (dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32)))
-            and (z is None or (z.stride(1) == 1 and z.dtype in (torch.bfloat16, torch.float32) and (decay is not None or z.dtype == dt_raw.dtype)))):
+            and (fixed or (dt_raw.stride(1) == 1 and dt_raw.dtype in (torch.bfloat16, torch.float32)))
+            and (gates is None or (gates.dtype == torch.float32 and gates.is_contiguous()))
+            and (z is None or (z.stride(1) == 1 and z.dtype in (torch.bfloat16, torch.float32) and (fixed or z.dtype == dt_raw.dtype)))):
         out = torch.empty(u.shape[0], H * P, dtype=torch.float32, device=u.device)
         f = lambda t: None if t is None else t.float().contiguous()
-        if decay is not None:
-            torch.ops.sglb.mamba2_scan(u, z, None, None, None, f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, f(decay))
+        if gates is not None:
+            torch.ops.sglb.mamba2_scan(u, z, None, None, None, f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, None, gates)
+        elif decay is not None:
+            torch.ops.sglb.mamba2_scan(u, z, None, None, None, f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, f(decay), None)
         else:
-            torch.ops.sglb.mamba2_scan(u, z, dt_raw, f(dt_bias), f(A_log), f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, None)
+            torch.ops.sglb.mamba2_scan(u, z, dt_raw, f(dt_bias), f(A_log), f(D), state, req_slots, seq_lens, cu_q, int(H), int(P), int(N), int(G), out, None, None)
         return out
-    return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G, decay)
+    return torch_ref.mamba2_scan(u, z, dt_raw, dt_bias, A_log, D, state, req_slots, seq_lens, q_lens, H, P, N, G, decay, gates)
 
 
 def attention_sink_gate(o: torch.Tensor, lse: torch.Tensor, sinks: torch.Tensor, Dv: Optional[int] = None) -> torch.Tensor:
@@ -671,21 +678,25 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 # ------------------------------------------------------------------ attention preparation / selective scan / element-wise activations
 def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       out_cache_loc: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
-                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0) -> torch.Tensor:
+                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0,
+                      v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
     """what lies between the q / k / v projection and the attention kernel, in one pass per token: an RMS norm of q and of k over their whole
     projection with a weight, a rotation of the first coordinates of every head by position (pairs half a rotary width apart, angles in
     fp32 from ``inv_freq``), a blend of v with another layer's values of the same token, and the write of k / v rows into the paged cache
     (csrc/kernels/window_attention.cu; semantics in ``torch_ref.attention_prepare``).  ``qkv`` may be the first columns of a wider
-    projection; ``v_first`` may be a column view.  Returns q [T, H, D | pad] in the cache dtype."""
+    projection; ``v_first`` may be a column view.  ``v_inv_freq`` fp32 [Dv/2]: every value head is also turned over its whole width by
+    ``position * v_inv_freq[m]`` before it is cached (pairs half a head apart, or neighbours with ``v_interleaved``).  Returns q [T, H, D | pad]
+    in the cache dtype."""
     if (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float32) and qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
             and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 and k_cache.stride(0) == v_cache.stride(0)
             and (v_first is None or (v_first.dtype == qkv.dtype and v_first.stride(1) == 1))
             and (q_norm_w is None or (q_norm_w.dtype == qkv.dtype and k_norm_w.dtype == qkv.dtype))):
         q = torch.empty(qkv.shape[0], H, pad if pad > 0 else D, dtype=qkv.dtype, device=qkv.device)
         torch.ops.sglb.attention_prepare(qkv, int(H), int(G), int(D), int(Dv), positions, k_cache, v_cache, out_cache_loc, q_norm_w, k_norm_w, float(eps),
-                                         inv_freq, v_first, float(v_lambda), q, int(pad))
+                                         inv_freq, v_first, float(v_lambda), q, int(pad), v_inv_freq, bool(v_interleaved))
         return q
-    return torch_ref.attention_prepare(qkv, H, G, D, Dv, positions, k_cache, v_cache, out_cache_loc, q_norm_w, k_norm_w, eps, inv_freq, v_first, v_lambda, pad)
+    return torch_ref.attention_prepare(qkv, H, G, D, Dv, positions, k_cache, v_cache, out_cache_loc, q_norm_w, k_norm_w, eps, inv_freq, v_first, v_lambda, pad,
+                                       v_inv_freq, v_interleaved)
 
 
 def mamba1_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
@@ -717,3 +728,110 @@ def activation(x: torch.Tensor, kind: str, out_dtype: Optional[torch.dtype] = No
     xf = x.float()
     y = torch.nn.functional.silu(xf) if kind == "silu" else torch.nn.functional.gelu(xf, approximate="tanh")
     return y.to(out_dtype)
+
+
+# ------------------------------------------------------------------ rotated values / parallel blocks / rotary latent attention / exponentially gated matrix memory
+def rotate_heads(o: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, Dv: int, interleaved: bool = False, inverse: bool = True,
+                 lse: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o [T, H, >= Dv] -> [T, H * Dv]: the heads of an attention output turned over their whole width by ``-+ position * inv_freq[m]`` (fp32
+    angle, sine and cosine; pairs half a head apart or, ``interleaved``, neighbours), after ``o * sigmoid(lse - sink_h)`` when the attention
+    returned the log-sum-exp of its scores; drops zero padding behind ``Dv`` (csrc/kernels/window_attention.cu).  Values cached with the
+    rotation of their own position (``attention_prepare(v_inv_freq=...)``) come out relative to the query's."""
+    T, H = o.shape[0], o.shape[1]
+    if (_use_native(o) and o.dtype in (torch.bfloat16, torch.float32) and o.is_contiguous() and Dv % 2 == 0
+            and (lse is None or (lse.dtype == torch.float32 and lse.is_contiguous()))):
+        if out is None:
+            out = torch.empty(T, H * Dv, dtype=o.dtype, device=o.device)
+        assert out.dtype == o.dtype and out.is_contiguous()
+        torch.ops.sglb.rotate_heads(o, positions, inv_freq, int(Dv), bool(interleaved), bool(inverse), lse,
+                                    None if lse is None else sinks.float().contiguous(), out)
+        return out
+    y = torch_ref.rotate_heads(o, positions, inv_freq, Dv, interleaved, inverse, lse, sinks)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def parallel_add_rmsnorm_f32(residual: torch.Tensor, deltas, w1: torch.Tensor, w2: Optional[torch.Tensor], eps: float, zero_centred: bool = False,
+                             out_dtype: torch.dtype = torch.bfloat16, extra: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """fp32 residual stream of blocks whose branches read the same input: ``residual += sum(deltas) + extra`` (in place; ``deltas``: up to two
+    branch outputs in the model dtype, ``extra``: one fp32 tensor, e.g. an embedding added again) and the RMS norm of the new residual under
+    TWO weights (the second may be None), one kernel (csrc/kernels/residual_f32.cu).  Returns (norm * g(w1), norm * g(w2) | None) in
+    ``out_dtype``."""
+    deltas = [d for d in deltas if d is not None]
+    if (_use_native(residual) and residual.dtype == torch.float32 and residual.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32)
+            and len(deltas) <= 2 and all(d.dtype == out_dtype and d.is_contiguous() for d in deltas)
+            and (extra is None or (extra.dtype == torch.float32 and extra.is_contiguous())) and w1.dtype == out_dtype
+            and (w2 is None or w2.dtype == out_dtype)):
+        o1 = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        o2 = torch.empty_like(o1) if w2 is not None else None
+        torch.ops.sglb.parallel_add_rmsnorm_f32(residual, deltas[0] if deltas else None, deltas[1] if len(deltas) > 1 else None, extra, w1, w2, o1, o2,
+                                                float(eps), bool(zero_centred))
+        return o1, o2
+    return torch_ref.parallel_add_rmsnorm_f32(residual, deltas + ([extra] if extra is not None else []), w1, w2, eps, zero_centred, out_dtype)
+
+
+def glu_activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """[gate | up] halves -> act(gate) * up with ``silu`` or ``gelu_tanh``, fp32 math, bf16 or fp32 tensors (csrc/kernels/elementwise.cu)"""
+    if _use_native(x) and x.dim() == 2 and x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float32) and x.shape[1] % 2 == 0:
+        out = torch.empty(x.shape[0], x.shape[1] // 2, dtype=x.dtype, device=x.device)
+        torch.ops.sglb.glu_activation(x, {"silu": 0, "gelu_tanh": 2}[kind], out)
+        return out
+    return torch_ref.glu_activation(x, kind)
+
+
+def latent_prepare(x: torch.Tensor, q_rank: int, q_norm_w: Optional[torch.Tensor], rank: int, rot_dim: int, kv_norm_w: torch.Tensor, eps: float,
+                   positions: torch.Tensor, inv_freq: Optional[torch.Tensor], mult: float, cache: torch.Tensor,
+                   out_cache_loc: torch.Tensor) -> Optional[torch.Tensor]:
+    """what lies behind the down-projections of latent attention, one pass per token: RMS norm of the query latent (returned) and of the
+    key / value latent (into the first ``rank`` columns of the token's cache row), and the shared rotary key turned by position into the
+    next ``rot_dim`` columns (csrc/kernels/latent_attention.cu; semantics in ``torch_ref.latent_prepare``).  ``x`` may be a column view."""
+    if (_use_native(x) and x.dtype in (torch.bfloat16, torch.float32) and x.stride(1) == 1 and cache.dtype == x.dtype and cache.stride(-1) == 1
+            and kv_norm_w.dtype == x.dtype and (q_norm_w is None or q_norm_w.dtype == x.dtype) and rot_dim % 2 == 0):
+        cq = torch.empty(x.shape[0], q_rank, dtype=x.dtype, device=x.device) if q_rank > 0 else None
+        torch.ops.sglb.latent_prepare(x, int(q_rank), q_norm_w, int(rank), int(rot_dim), kv_norm_w, float(eps), positions, inv_freq, float(mult), cache,
+                                      out_cache_loc, cq)
+        return cq
+    return torch_ref.latent_prepare(x, q_rank, q_norm_w, rank, rot_dim, kv_norm_w, eps, positions, inv_freq, mult, cache, out_cache_loc)
+
+
+def latent_query(q: torch.Tensor, q_abs: torch.Tensor, dim: int, rot_dim: int, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                 mult: float = 1.0) -> torch.Tensor:
+    """assembles the query of absorbed latent attention with a rotary part: [q_abs (fp32 [H, T, rank]) | rotary columns of q turned by
+    position] -> fp32 [T, H, rank + rot_dim] (csrc/kernels/latent_attention.cu; semantics in ``torch_ref.latent_query``)"""
+    if (_use_native(q) and q.dtype in (torch.bfloat16, torch.float32) and q.is_contiguous() and q_abs.dtype == torch.float32 and q_abs.is_contiguous()
+            and rot_dim % 2 == 0):
+        T, H = q.shape[0], q.shape[1]
+        out = torch.empty(T, H, q_abs.shape[2] + rot_dim, dtype=torch.float32, device=q.device)
+        torch.ops.sglb.latent_query(q, q_abs, int(dim), int(rot_dim), positions, inv_freq, float(mult), out)
+        return out
+    return torch_ref.latent_query(q, q_abs, dim, rot_dim, positions, inv_freq, mult)
+
+
+def mlstm_prepare(proj: torch.Tensor, gates_raw: torch.Tensor, H: int, D: int, Dv: int, cap: float, mstate: torch.Tensor, req_slots: torch.Tensor,
+                  seq_lens: torch.Tensor, cu_q: Optional[torch.Tensor], q_lens: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """inputs of the exponentially gated matrix memory (mLSTM) for ``mamba2_scan(gates=...)``: the scan's [x | B | C] rows in fp32 (values with
+    a column of ones per head, keys, scaled queries) and, from the capped gate pre-activations and the running maximum carried in ``mstate``,
+    every token's (decay, input scale, denominator floor) (csrc/kernels/mamba.cu; semantics in ``torch_ref.mlstm_prepare``).  ``proj`` may be
+    a column view of a wider projection."""
+    if (_use_native(proj) and proj.dtype in (torch.bfloat16, torch.float32) and proj.stride(1) == 1 and gates_raw.dtype == torch.float32
+            and gates_raw.is_contiguous() and mstate.dtype == torch.float32 and mstate.is_contiguous() and req_slots.numel() <= 65535):
+        T = proj.shape[0]
+        u = torch.empty(T, H * (Dv + 1) + 2 * H * D, dtype=torch.float32, device=proj.device)
+        gates = torch.empty(T, H, 3, dtype=torch.float32, device=proj.device)
+        torch.ops.sglb.mlstm_prepare(proj, gates_raw, int(H), int(D), int(Dv), float(cap), mstate, req_slots, seq_lens, cu_q, u, gates)
+        return u, gates
+    return torch_ref.mlstm_prepare(proj, gates_raw, H, D, Dv, cap, mstate, req_slots, seq_lens, q_lens)
+
+
+def mlstm_readout(y: torch.Tensor, gates: torch.Tensor, H: int, Dv: int, norm_w: torch.Tensor, eps: float, gate: Optional[torch.Tensor],
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """read-out of the exponentially gated matrix memory: division by the floored normaliser, per-head unit RMS, weight, sigmoid gate, cast
+    (csrc/kernels/mamba.cu; semantics in ``torch_ref.mlstm_readout``).  ``gate`` may be a column view."""
+    if (_use_native(y) and y.dtype == torch.float32 and y.is_contiguous() and gates.dtype == torch.float32 and gates.is_contiguous()
+            and out_dtype in (torch.bfloat16, torch.float32) and norm_w.dtype == out_dtype and (gate is None or (gate.dtype == out_dtype and gate.stride(1) == 1))):
+        out = torch.empty(y.shape[0], H * Dv, dtype=out_dtype, device=y.device)
+        torch.ops.sglb.mlstm_readout(y, gates, int(H), int(Dv), norm_w, float(eps), gate, out)
+        return out
+    return torch_ref.mlstm_readout(y, gates, H, Dv, norm_w, eps, gate, out_dtype)

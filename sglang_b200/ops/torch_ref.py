@@ -398,12 +398,16 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.T
 
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_table: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor,
-                     q_lens: Optional[torch.Tensor], page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor]) -> torch.Tensor:
+                     q_lens: Optional[torch.Tensor], page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor],
+                     v_rank: Optional[int] = None) -> torch.Tensor:
     """absorbed multi-query attention over cached latent rows.  q_lat fp32 [T, H, rank] (query already multiplied into the key up-projection);
     cache [slots, 1, >= rank]; key j of a request is visible to its query i when ``0 <= i - j < window`` (``window <= 0``: all earlier keys);
-    ``sinks`` fp32 [H]: exp(sink_h) joins the soft-max denominator only.  Returns the probability-weighted latent rows, fp32 [T, H, rank]."""
+    ``sinks`` fp32 [H]: exp(sink_h) joins the soft-max denominator only.  Returns the probability-weighted latent rows, fp32 [T, H, rank].
+    ``v_rank < rank``: only the first ``v_rank`` columns of a row are its value (the rest, e.g. a rotary key part, only score); the result is
+    [T, H, v_rank]."""
     T, H, R = q_lat.shape
-    out = torch.empty(T, H, R, dtype=torch.float32, device=q_lat.device)
+    Rv = R if v_rank is None else int(v_rank)
+    out = torch.empty(T, H, Rv, dtype=torch.float32, device=q_lat.device)
     qs = 0
     for b in range(req_slots.shape[0]):
         L = int(seq_lens[b])
@@ -423,7 +427,7 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, rank: int, page_t
         if sinks is not None:
             s = torch.cat([s, sinks.float()[:, None, None].expand(H, ql, 1)], -1)
         p = torch.softmax(s, dim=-1)[..., : pos.numel()]
-        out[qs:qs + ql] = torch.einsum("hqk,kr->qhr", p, C)
+        out[qs:qs + ql] = torch.einsum("hqk,kr->qhr", p, C[:, :Rv])
         qs += ql
     return out
 
@@ -532,9 +536,10 @@ def grouped_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: flo
 
 def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: Optional[torch.Tensor],
                 state: torch.Tensor, req_slots: torch.Tensor, seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor], H: int, P: int, N: int,
-                G: int, decay: Optional[torch.Tensor] = None) -> torch.Tensor:
+                G: int, decay: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Mamba-2 recurrence over a ragged batch, token by token, state in place.  ``decay`` fp32 [H] (then ``dt_raw``, ``dt_bias`` and ``A_log``
     are not read): the step size is 1 and every head's state shrinks by its constant, S <- decay_h S + B x^T (linear attention with decay).
+    ``gates`` fp32 [T, H, >= 2] (likewise): every token brings its own decay ``gates[t, h, 0]`` and step ``gates[t, h, 1]``.
 
     u fp32 [T, H*P + 2*G*N] = short-conv outputs [x | B | C]; head h reads B / C group ``h // (H // G)``.  dt = softplus(dt_raw + dt_bias) [T, H]
     (no clamp).  state fp32 [slots, H, N, P]; a request whose ``seq_len == q_len`` starts from zero.  Per token and head:
@@ -545,7 +550,9 @@ def mamba2_scan(u: torch.Tensor, z: Optional[torch.Tensor], dt_raw: torch.Tensor
     x = u[:, :inner].float().view(T, H, P)
     Bm = u[:, inner:inner + G * N].float().view(T, G, N).repeat_interleave(rep, 1)
     Cm = u[:, inner + G * N:inner + 2 * G * N].float().view(T, G, N).repeat_interleave(rep, 1)
-    if decay is not None:
+    if gates is not None:
+        dA, dt = gates[:, :, 0].float(), gates[:, :, 1].float()
+    elif decay is not None:
         dt = torch.ones(T, H, dtype=torch.float32, device=u.device)
         dA = decay.float()[None, :].expand(T, H)
     else:
@@ -673,14 +680,17 @@ def softmax_bias_route(logits: torch.Tensor, correction: Optional[torch.Tensor],
 # ------------------------------------------------------------------ Resatar mechanisms: attention preparation (projection-wide norm, partial rotation, value mixing), selective scan
 def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       out_cache_loc: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
-                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0) -> torch.Tensor:
+                      inv_freq: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, v_lambda: float = 0.0, pad: int = 0,
+                      v_inv_freq: Optional[torch.Tensor] = None, v_interleaved: bool = False) -> torch.Tensor:
     """rows of ``qkv`` [T, >= H*D + G*D + G*Dv] = [q | k | v | ...] -> q [T, H, D] in the cache dtype; k rows to ``k_cache[loc]`` (first
     ``G*D`` columns), v rows to ``v_cache[loc]`` (first ``G*Dv`` columns).  In this order:
 
     * ``q_norm_w`` [H*D] / ``k_norm_w`` [G*D]: q and k are RMS-normed over their WHOLE projection (all heads at once), times the weight;
     * ``inv_freq`` fp32 [R/2]: the first R coordinates of every q and k head are rotated by the angle ``position * inv_freq[i]``, coordinate
       ``i`` paired with ``i + R/2``;
-    * ``v_first`` [T, G*Dv]: v <- (1 - v_lambda) v + v_lambda v_first before it is cached.
+    * ``v_first`` [T, G*Dv]: v <- (1 - v_lambda) v + v_lambda v_first before it is cached;
+    * ``v_inv_freq`` fp32 [Dv/2]: every value head is rotated over its whole width by ``position * v_inv_freq[m]`` before it is cached, pair m
+      = coordinates ``(m, m + Dv/2)``, or ``(2m, 2m + 1)`` with ``v_interleaved`` (``rotate_heads`` turns an attention output back).
 
     ``pad > 0``: every head of q, k and v occupies ``pad`` columns, zeros behind its values (q is [T, H, pad])."""
     T = qkv.shape[0]
@@ -703,6 +713,8 @@ def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positi
         q, k = rot(q), rot(k)
     if v_first is not None:
         v = (1.0 - v_lambda) * v + v_lambda * v_first.float()
+    if v_inv_freq is not None:
+        v = rotate_pairs(v.reshape(T, G, Dv), positions, v_inv_freq, v_interleaved).reshape(T, G * Dv)
     loc = out_cache_loc.long()
     if pad > 0:
         zp = lambda t, n: torch.nn.functional.pad(t, (0, pad - n))
@@ -712,6 +724,146 @@ def attention_prepare(qkv: torch.Tensor, H: int, G: int, D: int, Dv: int, positi
     k_cache[loc, 0, :G * D] = k.reshape(T, G * D).to(k_cache.dtype)
     v_cache[loc, 0, :G * Dv] = v.to(v_cache.dtype)
     return q.to(k_cache.dtype)
+
+
+def rotate_pairs(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, interleaved: bool, inverse: bool = False,
+                 mult: float = 1.0) -> torch.Tensor:
+    """x fp32 [T, heads, n]: the first ``2 * len(inv_freq)`` coordinates of every head turned by ``position * inv_freq[m]`` (``inverse``: by the
+    negative angle), pair m = coordinates ``(m, m + half)`` or, ``interleaved``, ``(2m, 2m + 1)``; sine and cosine both times ``mult``; the
+    angle is the fp32 product"""
+    half = inv_freq.numel()
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]
+    c, s = (torch.cos(ang) * mult)[:, None, :], (torch.sin(ang) * mult)[:, None, :]
+    if inverse:
+        s = -s
+    if interleaved:
+        a, b = x[..., 0:2 * half:2], x[..., 1:2 * half:2]
+        r = torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2)
+        return torch.cat([r, x[..., 2 * half:]], -1)
+    a, b = x[..., :half], x[..., half:2 * half]
+    return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * half:]], -1)
+
+
+def rotate_heads(o: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, Dv: int, interleaved: bool, inverse: bool,
+                 lse: Optional[torch.Tensor], sinks: Optional[torch.Tensor]) -> torch.Tensor:
+    """o [T, H, >= Dv] -> [T, H * Dv] in o's dtype: ``o[:, :, :Dv]``, times ``sigmoid(lse - sink_h)`` when the attention returned its
+    log-sum-exp (a sink joins the denominator), every head then turned over its whole width by ``-+ position * inv_freq[m]``"""
+    T, H = o.shape[0], o.shape[1]
+    x = o[:, :, :Dv].float()
+    if lse is not None:
+        x = x * torch.sigmoid(lse.float() - sinks.float()[None, :]).unsqueeze(-1)
+    return rotate_pairs(x, positions, inv_freq, interleaved, inverse).reshape(T, H * Dv).to(o.dtype)
+
+
+def parallel_add_rmsnorm_f32(residual: torch.Tensor, deltas, w1: torch.Tensor, w2: Optional[torch.Tensor], eps: float, zero_centred: bool,
+                             out_dtype: torch.dtype):
+    """residual (fp32, in place) += sum of ``deltas`` (fp32 sum of the deltas first); returns the RMS norm of the new residual under ``w1``
+    and, when given, under ``w2`` (weights applied as ``1 + w`` when ``zero_centred``), both in ``out_dtype``"""
+    if deltas:
+        d = deltas[0].float()
+        for t in deltas[1:]:
+            d = d + t.float()
+        residual.add_(d)
+    y = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
+    g = (lambda w: 1.0 + w.float()) if zero_centred else (lambda w: w.float())
+    return (y * g(w1)).to(out_dtype), ((y * g(w2)).to(out_dtype) if w2 is not None else None)
+
+
+def glu_activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """x [T, 2F] = [gate | up] -> act(gate) * up, fp32 math, x's dtype; ``kind``: ``silu`` or ``gelu_tanh``"""
+    F_ = x.shape[-1] // 2
+    g, u = x[..., :F_].float(), x[..., F_:].float()
+    a = F.silu(g) if kind == "silu" else F.gelu(g, approximate="tanh")
+    return (a * u).to(x.dtype)
+
+
+def latent_prepare(x: torch.Tensor, q_rank: int, q_norm_w: Optional[torch.Tensor], rank: int, rot_dim: int, kv_norm_w: torch.Tensor, eps: float,
+                   positions: torch.Tensor, inv_freq: Optional[torch.Tensor], mult: float, cache: torch.Tensor,
+                   out_cache_loc: torch.Tensor) -> Optional[torch.Tensor]:
+    """rows of ``x`` [T, >= q_rank + rank + rot_dim] = [query latent | key/value latent | shared rotary key]: the query latent RMS-normed times
+    ``q_norm_w`` is returned in x's dtype (``q_rank = 0``: none); the key/value latent RMS-normed times ``kv_norm_w`` goes to the first ``rank``
+    columns of ``cache[loc]`` and the rotary key, turned by ``position * inv_freq[m]`` on neighbouring pairs ``(2m, 2m + 1)`` with sine and
+    cosine times ``mult``, to the next ``rot_dim`` columns (cache [slots, 1, width])"""
+    T = x.shape[0]
+    xf = x.float()
+    nrm = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+    c = nrm(xf[:, q_rank:q_rank + rank]) * kv_norm_w.float()
+    loc = out_cache_loc.long()
+    cache[loc, 0, :rank] = c.to(cache.dtype)
+    if rot_dim > 0:
+        kr = xf[:, q_rank + rank:q_rank + rank + rot_dim].reshape(T, 1, rot_dim)
+        if inv_freq is not None:
+            kr = rotate_pairs(kr, positions, inv_freq, True, False, mult)
+        cache[loc, 0, rank:rank + rot_dim] = kr.reshape(T, rot_dim).to(cache.dtype)
+    if q_rank > 0:
+        return (nrm(xf[:, :q_rank]) * q_norm_w.float()).to(x.dtype)
+    return None
+
+
+def latent_query(q: torch.Tensor, q_abs: torch.Tensor, dim: int, rot_dim: int, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                 mult: float) -> torch.Tensor:
+    """the query of absorbed latent attention with a rotary part: q [T, H, dim + rot_dim] (per head: unrotated | rotary), ``q_abs`` fp32
+    [H, T, rank] (the unrotated part already multiplied into the key up-projection) -> fp32 [T, H, rank + rot_dim] = [q_abs | rotary part
+    turned by position (neighbouring pairs, sine and cosine times ``mult``)]"""
+    qr = q[:, :, dim:dim + rot_dim].float()
+    if inv_freq is not None:
+        qr = rotate_pairs(qr, positions, inv_freq, True, False, mult)
+    return torch.cat([q_abs.float().transpose(0, 1), qr], -1).contiguous()
+
+
+def mlstm_prepare(proj: torch.Tensor, gates_raw: torch.Tensor, H: int, D: int, Dv: int, cap: float, mstate: torch.Tensor, req_slots: torch.Tensor,
+                  seq_lens: torch.Tensor, q_lens: Optional[torch.Tensor]):
+    """inputs of the matrix-memory recurrence with exponential gates and a running maximum (mLSTM), ragged over requests.
+
+    ``proj`` [T, >= 2*H*D + H*Dv] = [q | k | v | ...]; ``gates_raw`` fp32 [T, 2H] = [input | forget] pre-activations.  Per head:
+    ``i = cap tanh(raw_i / cap)``, ``f = logsigmoid(cap tanh(raw_f / cap))`` (``cap <= 0``: no cap), ``m_t = max(f + m_(t-1), i)`` with m = 0
+    at the start of a sequence (``mstate`` fp32 [slots, H] carries it from call to call, in place).  Returns
+
+    * u fp32 [T, H*(Dv+1) + 2*H*D] = [v with a column of ones behind every head | k | q / sqrt(D)]: the scan's [x | B | C] (the ones
+      column accumulates the normaliser n alongside the memory);
+    * gates fp32 [T, H, 3] = (exp(f + m_(t-1) - m_t), exp(i - m_t), exp(-m_t)): decay, input scale and the floor of the denominator."""
+    T = proj.shape[0]
+    q = proj[:, :H * D].float() * (D ** -0.5)
+    k = proj[:, H * D:2 * H * D].float()
+    v = proj[:, 2 * H * D:2 * H * D + H * Dv].float().view(T, H, Dv)
+    x = torch.cat([v, torch.ones(T, H, 1, dtype=torch.float32, device=proj.device)], -1).reshape(T, H * (Dv + 1))
+    u = torch.cat([x, k, q], -1).contiguous()
+    raw = gates_raw.float()
+    capf = (lambda t: cap * torch.tanh(t / cap)) if cap > 0 else (lambda t: t)
+    ig = capf(raw[:, :H])
+    fg = F.logsigmoid(capf(raw[:, H:2 * H]))
+    gates = torch.empty(T, H, 3, dtype=torch.float32, device=proj.device)
+    off = 0
+    for b in range(req_slots.shape[0]):
+        n = 1 if q_lens is None else int(q_lens[b])
+        if n <= 0:
+            continue
+        slot = int(req_slots[b])
+        m = torch.zeros(H, dtype=torch.float32, device=proj.device) if int(seq_lens[b]) - n == 0 else mstate[slot].clone()
+        for t in range(off, off + n):
+            m_new = torch.maximum(fg[t] + m, ig[t])
+            gates[t, :, 0] = torch.exp(fg[t] + m - m_new)
+            gates[t, :, 1] = torch.exp(ig[t] - m_new)
+            gates[t, :, 2] = torch.exp(-m_new)
+            m = m_new
+        mstate[slot] = m
+        off += n
+    return u, gates
+
+
+def mlstm_readout(y: torch.Tensor, gates: torch.Tensor, H: int, Dv: int, norm_w: torch.Tensor, eps: float, gate: Optional[torch.Tensor],
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """y fp32 [T, H*(Dv+1)]: per head the memory's read-out and, in the last column, the normaliser's (n . q).  Per head
+    ``o = y[:Dv] / (max(|n . q|, gates[..., 2]) + 1e-6)``, divided by its root mean square, times ``norm_w`` [H*Dv], times ``sigmoid(gate)``
+    ([T, H*Dv]) -> [T, H*Dv] in ``out_dtype``"""
+    T = y.shape[0]
+    yy = y.float().view(T, H, Dv + 1)
+    den = torch.maximum(yy[..., Dv].abs(), gates[..., 2].float()) + 1e-6
+    o = yy[..., :Dv] / den[..., None]
+    o = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, H * Dv) * norm_w.float()
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    return o.to(out_dtype)
 
 
 def mamba1_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A_log: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
