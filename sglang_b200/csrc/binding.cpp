@@ -345,12 +345,17 @@ void grouped_rmsnorm(const at::Tensor& x, const at::Tensor& w, int64_t groups, d
 
 void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, c10::optional<at::Tensor> dt_raw, c10::optional<at::Tensor> dt_bias,
                  c10::optional<at::Tensor> A_log, c10::optional<at::Tensor> D, at::Tensor state, const at::Tensor& req_slots, const at::Tensor& seq_lens,
-                 c10::optional<at::Tensor> cu_q, int64_t H, int64_t P, int64_t N, int64_t G, at::Tensor out, c10::optional<at::Tensor> decay) {
+                 c10::optional<at::Tensor> cu_q, int64_t H, int64_t P, int64_t N, int64_t G, at::Tensor out, c10::optional<at::Tensor> decay,
+                 c10::optional<at::Tensor> gates) {
   CHECK_CUDA(u); CHECK_I32(req_slots); CHECK_I32(seq_lens);
   auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
   TORCH_CHECK(f32c(u) && f32c(state) && f32c(out) && u.dim() == 2 && u.size(1) >= H * P + 2 * G * N);
   bool in_bf16 = false;
-  if (decay.has_value()) {          // constant decay per head, step size 1: no step-size inputs
+  const bool fixed = decay.has_value() || gates.has_value();
+  if (gates.has_value()) {          // every token brings its decay and step: no step-size inputs
+    TORCH_CHECK(!decay.has_value() && f32c(*gates) && gates->dim() == 3 && gates->size(0) == u.size(0) && gates->size(1) == H && gates->size(2) >= 2);
+    if (z.has_value()) in_bf16 = z->scalar_type() == at::kBFloat16;
+  } else if (decay.has_value()) {          // constant decay per head, step size 1: no step-size inputs
     TORCH_CHECK(f32c(*decay) && decay->numel() == H);
     if (z.has_value()) in_bf16 = z->scalar_type() == at::kBFloat16;
   } else {
@@ -368,10 +373,10 @@ void mamba2_scan(const at::Tensor& u, c10::optional<at::Tensor> z, c10::optional
   if (u.size(0) == 0) return;
   c10::cuda::CUDAGuard g(u.device());
   sglb::mamba2_scan(u.data_ptr<float>(), (int)u.stride(0), z.has_value() ? z->data_ptr() : nullptr, z.has_value() ? (int)z->stride(0) : 0,
-                    decay.has_value() ? nullptr : dt_raw->data_ptr(), decay.has_value() ? 0 : (int)dt_raw->stride(0), in_bf16,
-                    decay.has_value() ? nullptr : dt_bias->data_ptr<float>(), decay.has_value() ? nullptr : A_log->data_ptr<float>(), opt_ptr<float>(D),
+                    fixed ? nullptr : dt_raw->data_ptr(), fixed ? 0 : (int)dt_raw->stride(0), in_bf16,
+                    fixed ? nullptr : dt_bias->data_ptr<float>(), fixed ? nullptr : A_log->data_ptr<float>(), opt_ptr<float>(D),
                     state.data_ptr<float>(), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q), B, (int)H, (int)P, (int)N, (int)G,
-                    out.data_ptr<float>(), opt_ptr<float>(decay), cur_stream());
+                    out.data_ptr<float>(), opt_ptr<float>(decay), opt_ptr<float>(gates), gates.has_value() ? (int)gates->size(2) : 0, cur_stream());
   count();
 }
 
@@ -457,7 +462,8 @@ void mamba1_scan(const at::Tensor& u, const at::Tensor& dt_raw, c10::optional<at
 
 void attention_prepare(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D, int64_t Dv, const at::Tensor& positions, at::Tensor k_cache, at::Tensor v_cache,
                        const at::Tensor& loc, c10::optional<at::Tensor> q_norm_w, c10::optional<at::Tensor> k_norm_w, double eps,
-                       c10::optional<at::Tensor> inv_freq, c10::optional<at::Tensor> v_first, double v_lambda, at::Tensor q_out, int64_t pad) {
+                       c10::optional<at::Tensor> inv_freq, c10::optional<at::Tensor> v_first, double v_lambda, at::Tensor q_out, int64_t pad,
+                       c10::optional<at::Tensor> v_inv_freq, bool v_interleaved) {
   CHECK_CUDA(qkv); CHECK_I32(positions); CHECK_I32(loc);
   const int64_t T = qkv.size(0);
   TORCH_CHECK(bf16_or_f32(qkv) && qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) >= H * D + G * D + G * Dv && H % G == 0);
@@ -479,13 +485,15 @@ void attention_prepare(const at::Tensor& qkv, int64_t H, int64_t G, int64_t D, i
   if (v_first.has_value())
     TORCH_CHECK(v_first->scalar_type() == qkv.scalar_type() && v_first->dim() == 2 && v_first->stride(1) == 1 && v_first->size(0) == T &&
                 v_first->size(1) == G * Dv);
+  if (v_inv_freq.has_value())
+    TORCH_CHECK(v_inv_freq->scalar_type() == at::kFloat && v_inv_freq->is_contiguous() && Dv % 2 == 0 && v_inv_freq->numel() == Dv / 2);
   if (T == 0) return;
   c10::cuda::CUDAGuard g(qkv.device());
   sglb::attention_prepare(qkv.data_ptr(), (int)qkv.stride(0), qkv.scalar_type() == at::kBFloat16, (int)T, (int)H, (int)G, (int)D, (int)Dv,
                           positions.data_ptr<int>(), q_norm_w.has_value() ? q_norm_w->data_ptr() : nullptr, k_norm_w.has_value() ? k_norm_w->data_ptr() : nullptr,
                           (float)eps, half > 0 ? inv_freq->data_ptr<float>() : nullptr, half, v_first.has_value() ? v_first->data_ptr() : nullptr,
                           v_first.has_value() ? (int)v_first->stride(0) : 0, (float)v_lambda, k_cache.data_ptr(), v_cache.data_ptr(), (size_t)k_cache.stride(0),
-                          loc.data_ptr<int>(), q_out.data_ptr(), (int)pad, cur_stream());
+                          loc.data_ptr<int>(), q_out.data_ptr(), (int)pad, opt_ptr<float>(v_inv_freq), v_interleaved, cur_stream());
   count();
 }
 
@@ -502,13 +510,15 @@ void sigmoid_gate(const at::Tensor& o, const at::Tensor& gate, int64_t Dv, doubl
   count();
 }
 
-void activation(const at::Tensor& x, int64_t act, at::Tensor out) {
+void activation(const at::Tensor& x, int64_t act, at::Tensor out, c10::optional<at::Tensor> mul) {
   CHECK_CUDA(x);
   TORCH_CHECK(bf16_or_f32(x) && bf16_or_f32(out) && x.dim() == 2 && x.stride(1) == 1 && out.is_contiguous() && out.numel() == x.numel() && (act == 0 || act == 2));
+  if (mul.has_value())
+    TORCH_CHECK(mul->scalar_type() == x.scalar_type() && mul->dim() == 2 && mul->stride(1) == 1 && mul->size(0) == x.size(0) && mul->size(1) == x.size(1));
   if (x.numel() == 0) return;
   c10::cuda::CUDAGuard g(x.device());
   sglb::activation(x.data_ptr(), (int)x.stride(0), x.scalar_type() == at::kBFloat16, out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)x.size(0),
-                   (int)x.size(1), (int)act, cur_stream());
+                   (int)x.size(1), (int)act, mul.has_value() ? mul->data_ptr() : nullptr, mul.has_value() ? (int)mul->stride(0) : 0, cur_stream());
   count();
 }
 
@@ -556,10 +566,11 @@ void moe_identity_shared_combine(at::Tensor y, const at::Tensor& h, c10::optiona
 
 void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank, const at::Tensor& page_table, const at::Tensor& req_slots,
                       const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, int64_t max_q_len, int64_t max_kv_len, int64_t page_size, double scale,
-                      int64_t window, c10::optional<at::Tensor> sinks, at::Tensor out) {
+                      int64_t window, c10::optional<at::Tensor> sinks, at::Tensor out, int64_t v_rank) {
   CHECK_CUDA(q); CHECK_I32(page_table); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  if (v_rank <= 0) v_rank = rank;
   TORCH_CHECK(q.scalar_type() == at::kFloat && q.dim() == 3 && q.is_contiguous() && out.scalar_type() == at::kFloat && out.is_contiguous() &&
-              out.numel() == q.numel() && q.size(2) == rank);
+              v_rank <= rank && out.numel() == q.size(0) * q.size(1) * v_rank && q.size(2) == rank);
   TORCH_CHECK((cache.scalar_type() == at::kFloat || cache.scalar_type() == at::kBFloat16) && cache.dim() == 3 && cache.size(1) == 1 &&
               cache.stride(2) == 1 && cache.size(2) >= rank && page_table.dim() == 2 && page_table.stride(1) == 1);
   const int B = (int)req_slots.size(0);
@@ -579,8 +590,126 @@ void latent_attention(const at::Tensor& q, const at::Tensor& cache, int64_t rank
   sglb::latent_attention(q.data_ptr<float>(), cache.data_ptr(), cache.scalar_type() == at::kBFloat16, (int)cache.stride(0), (int)rank,
                          page_table.data_ptr<int>(), (int)page_table.stride(0), (int)page_size, req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(),
                          opt_ptr<int>(cu_q), B, (int)max_q_len, (int)max_kv_len, (int)q.size(1), (float)scale, (int)window, opt_ptr<float>(sinks),
-                         out.data_ptr<float>(), decode ? ws.data_ptr<float>() : nullptr, ws_floats, cur_stream());
+                         out.data_ptr<float>(), decode ? ws.data_ptr<float>() : nullptr, ws_floats, (int)v_rank, cur_stream());
   count(decode ? 2 : 1);
+}
+
+void latent_prepare(const at::Tensor& x, int64_t q_rank, c10::optional<at::Tensor> q_norm_w, int64_t rank, int64_t rot_dim, const at::Tensor& kv_norm_w,
+                    double eps, const at::Tensor& positions, c10::optional<at::Tensor> inv_freq, double mult, at::Tensor cache, const at::Tensor& loc,
+                    c10::optional<at::Tensor> cq) {
+  CHECK_CUDA(x); CHECK_I32(positions); CHECK_I32(loc);
+  const int64_t T = x.size(0);
+  TORCH_CHECK(bf16_or_f32(x) && x.dim() == 2 && x.stride(1) == 1 && q_rank >= 0 && rank >= 1 && rot_dim >= 0 && rot_dim % 2 == 0 &&
+              x.size(1) >= q_rank + rank + rot_dim);
+  TORCH_CHECK(cache.scalar_type() == x.scalar_type() && cache.dim() == 3 && cache.size(1) == 1 && cache.stride(2) == 1 && cache.size(2) >= rank + rot_dim &&
+              positions.numel() == T && loc.numel() == T);
+  TORCH_CHECK(kv_norm_w.scalar_type() == x.scalar_type() && kv_norm_w.is_contiguous() && kv_norm_w.numel() == rank);
+  if (q_rank > 0)
+    TORCH_CHECK(q_norm_w.has_value() && cq.has_value() && q_norm_w->scalar_type() == x.scalar_type() && q_norm_w->is_contiguous() &&
+                q_norm_w->numel() == q_rank && cq->scalar_type() == x.scalar_type() && cq->is_contiguous() && cq->numel() == T * q_rank);
+  if (inv_freq.has_value()) TORCH_CHECK(inv_freq->scalar_type() == at::kFloat && inv_freq->is_contiguous() && 2 * inv_freq->numel() == rot_dim);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(x.device());
+  sglb::latent_prepare(x.data_ptr(), (int)x.stride(0), x.scalar_type() == at::kBFloat16, (int)T, (int)q_rank, q_rank > 0 ? q_norm_w->data_ptr() : nullptr,
+                       (int)rank, (int)rot_dim, kv_norm_w.data_ptr(), (float)eps, positions.data_ptr<int>(), opt_ptr<float>(inv_freq), (float)mult,
+                       cache.data_ptr(), (size_t)cache.stride(0), loc.data_ptr<int>(), q_rank > 0 ? cq->data_ptr() : nullptr, cur_stream());
+  count();
+}
+
+void latent_query(const at::Tensor& q, const at::Tensor& q_abs, int64_t dim, int64_t rot_dim, const at::Tensor& positions, c10::optional<at::Tensor> inv_freq,
+                  double mult, at::Tensor out) {
+  CHECK_CUDA(q); CHECK_I32(positions);
+  TORCH_CHECK(bf16_or_f32(q) && q.dim() == 3 && q.is_contiguous() && q.size(2) == dim + rot_dim && rot_dim % 2 == 0);
+  const int64_t T = q.size(0), H = q.size(1);
+  TORCH_CHECK(q_abs.scalar_type() == at::kFloat && q_abs.dim() == 3 && q_abs.is_contiguous() && q_abs.size(0) == H && q_abs.size(1) == T);
+  const int64_t R = q_abs.size(2);
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == T * H * (R + rot_dim) && positions.numel() == T);
+  if (inv_freq.has_value()) TORCH_CHECK(inv_freq->scalar_type() == at::kFloat && inv_freq->is_contiguous() && 2 * inv_freq->numel() == rot_dim);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(q.device());
+  sglb::latent_query(q.data_ptr(), q.scalar_type() == at::kBFloat16, q_abs.data_ptr<float>(), (int)T, (int)H, (int)dim, (int)rot_dim, (int)R,
+                     positions.data_ptr<int>(), opt_ptr<float>(inv_freq), (float)mult, out.data_ptr<float>(), cur_stream());
+  count();
+}
+
+void rotate_heads(const at::Tensor& o, const at::Tensor& positions, const at::Tensor& inv_freq, int64_t Dv, bool interleaved, bool inverse,
+                  c10::optional<at::Tensor> lse, c10::optional<at::Tensor> sinks, at::Tensor out) {
+  CHECK_CUDA(o); CHECK_I32(positions);
+  const int64_t T = o.size(0), H = o.size(1);
+  TORCH_CHECK(bf16_or_f32(o) && o.dim() == 3 && o.is_contiguous() && Dv >= 2 && Dv % 2 == 0 && Dv <= o.size(2) && out.scalar_type() == o.scalar_type() &&
+              out.is_contiguous() && out.numel() == T * H * Dv && positions.numel() == T && out.data_ptr() != o.data_ptr());
+  TORCH_CHECK(inv_freq.scalar_type() == at::kFloat && inv_freq.is_contiguous() && 2 * inv_freq.numel() == Dv);
+  TORCH_CHECK(lse.has_value() == sinks.has_value());
+  if (lse.has_value())
+    TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == T * H && sinks->scalar_type() == at::kFloat &&
+                sinks->is_contiguous() && sinks->numel() == H);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(o.device());
+  sglb::rotate_heads(o.data_ptr(), (int)o.size(2), o.scalar_type() == at::kBFloat16, positions.data_ptr<int>(), inv_freq.data_ptr<float>(), (int)T, (int)H,
+                     (int)Dv, interleaved, inverse, opt_ptr<float>(lse), opt_ptr<float>(sinks), out.data_ptr(), cur_stream());
+  count();
+}
+
+void parallel_add_rmsnorm_f32(at::Tensor residual, c10::optional<at::Tensor> d1, c10::optional<at::Tensor> d2, c10::optional<at::Tensor> d3, const at::Tensor& w1,
+                              c10::optional<at::Tensor> w2, at::Tensor out1, c10::optional<at::Tensor> out2, double eps, bool zero_centred) {
+  CHECK_CUDA(residual);
+  TORCH_CHECK(residual.scalar_type() == at::kFloat && residual.dim() == 2 && residual.is_contiguous() && bf16_or_f32(out1) && out1.is_contiguous() &&
+              out1.numel() == residual.numel() && w1.scalar_type() == out1.scalar_type() && w1.is_contiguous() && w1.numel() == residual.size(1));
+  TORCH_CHECK(w2.has_value() == out2.has_value());
+  if (w2.has_value())
+    TORCH_CHECK(w2->scalar_type() == out1.scalar_type() && w2->is_contiguous() && w2->numel() == residual.size(1) && out2->scalar_type() == out1.scalar_type() &&
+                out2->is_contiguous() && out2->numel() == residual.numel());
+  TORCH_CHECK(d1.has_value() || !d2.has_value());
+  bool dbf = out1.scalar_type() == at::kBFloat16;
+  if (d1.has_value()) {
+    TORCH_CHECK(bf16_or_f32(*d1) && d1->is_contiguous() && d1->numel() == residual.numel());
+    dbf = d1->scalar_type() == at::kBFloat16;
+  }
+  if (d2.has_value()) TORCH_CHECK(d2->scalar_type() == d1->scalar_type() && d2->is_contiguous() && d2->numel() == residual.numel());
+  if (d3.has_value()) TORCH_CHECK(d3->scalar_type() == at::kFloat && d3->is_contiguous() && d3->numel() == residual.numel());
+  if (residual.size(0) == 0) return;
+  c10::cuda::CUDAGuard g(residual.device());
+  sglb::parallel_add_rmsnorm_f32(residual.data_ptr<float>(), d1.has_value() ? d1->data_ptr() : nullptr, d2.has_value() ? d2->data_ptr() : nullptr, dbf,
+                                 opt_ptr<float>(d3), w1.data_ptr(), w2.has_value() ? w2->data_ptr() : nullptr, out1.data_ptr(),
+                                 out2.has_value() ? out2->data_ptr() : nullptr, out1.scalar_type() == at::kBFloat16, (int)residual.size(0),
+                                 (int)residual.size(1), (float)eps, zero_centred, cur_stream());
+  count();
+}
+
+void mlstm_prepare(const at::Tensor& proj, const at::Tensor& gates_raw, int64_t H, int64_t D, int64_t Dv, double cap, at::Tensor mstate,
+                   const at::Tensor& req_slots, const at::Tensor& seq_lens, c10::optional<at::Tensor> cu_q, at::Tensor u, at::Tensor gates) {
+  CHECK_CUDA(proj); CHECK_I32(req_slots); CHECK_I32(seq_lens);
+  const int64_t T = proj.size(0);
+  auto f32c = [](const at::Tensor& t) { return t.scalar_type() == at::kFloat && t.is_contiguous(); };
+  TORCH_CHECK(bf16_or_f32(proj) && proj.dim() == 2 && proj.stride(1) == 1 && proj.size(1) >= 2 * H * D + H * Dv);
+  TORCH_CHECK(f32c(gates_raw) && gates_raw.numel() == T * 2 * H && f32c(mstate) && mstate.dim() == 2 && mstate.size(1) == H && f32c(u) &&
+              u.numel() == T * (H * (Dv + 1) + 2 * H * D) && f32c(gates) && gates.numel() == T * H * 3);
+  const int B = (int)req_slots.size(0);
+  if (cu_q.has_value()) { CHECK_I32(*cu_q); TORCH_CHECK(cu_q->numel() == B + 1); } else TORCH_CHECK(T == B);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(proj.device());
+  sglb::mlstm_prepare(proj.data_ptr(), (int)proj.stride(0), proj.scalar_type() == at::kBFloat16, gates_raw.data_ptr<float>(), (int)T, B, (int)H, (int)D,
+                      (int)Dv, (float)cap, mstate.data_ptr<float>(), req_slots.data_ptr<int>(), seq_lens.data_ptr<int>(), opt_ptr<int>(cu_q),
+                      u.data_ptr<float>(), gates.data_ptr<float>(), cur_stream());
+  count();
+}
+
+void mlstm_readout(const at::Tensor& y, const at::Tensor& gates, int64_t H, int64_t Dv, const at::Tensor& norm_w, double eps, c10::optional<at::Tensor> gate,
+                   at::Tensor out) {
+  CHECK_CUDA(y);
+  const int64_t T = y.size(0);
+  TORCH_CHECK(y.scalar_type() == at::kFloat && y.is_contiguous() && y.numel() == T * H * (Dv + 1) && gates.scalar_type() == at::kFloat &&
+              gates.is_contiguous() && gates.numel() == T * H * 3);
+  TORCH_CHECK(bf16_or_f32(out) && out.is_contiguous() && out.numel() == T * H * Dv && norm_w.scalar_type() == out.scalar_type() && norm_w.is_contiguous() &&
+              norm_w.numel() == H * Dv);
+  if (gate.has_value())
+    TORCH_CHECK(gate->scalar_type() == out.scalar_type() && gate->dim() == 2 && gate->stride(1) == 1 && gate->size(0) == T && gate->size(1) == H * Dv);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard g(y.device());
+  sglb::mlstm_readout(y.data_ptr<float>(), gates.data_ptr<float>(), (int)T, (int)H, (int)Dv, norm_w.data_ptr(), (float)eps,
+                      gate.has_value() ? gate->data_ptr() : nullptr, gate.has_value() ? (int)gate->stride(0) : 0, out.data_ptr(),
+                      out.scalar_type() == at::kBFloat16, cur_stream());
+  count();
 }
 
 // bench tool: per-role cycle accounting of the decode attention kernel into buf [ctas * 30] (int64); an empty tensor turns it off
@@ -1001,13 +1130,14 @@ TORCH_LIBRARY(sglb, m) {
         &postnorm_add_rmsnorm_f32);
   m.def("grouped_rmsnorm(Tensor x, Tensor w, int groups, float eps, Tensor(a!) out, Tensor? gate=None, float out_scale=1.0) -> ()", &grouped_rmsnorm);
   m.def("mamba2_scan(Tensor u, Tensor? z, Tensor? dt_raw, Tensor? dt_bias, Tensor? A_log, Tensor? D, Tensor(a!) state, Tensor req_slots, Tensor seq_lens, "
-        "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out, Tensor? decay=None) -> ()", &mamba2_scan);
+        "Tensor? cu_q, int H, int P, int N, int G, Tensor(b!) out, Tensor? decay=None, Tensor? gates=None) -> ()", &mamba2_scan);
   m.def("mamba1_scan(Tensor u, Tensor dt_raw, Tensor? dt_bias, Tensor A_log, Tensor Bm, Tensor Cm, Tensor? D, Tensor? z, Tensor(a!) state, Tensor req_slots, "
         "Tensor seq_lens, Tensor? cu_q, Tensor(b!) out) -> ()", &mamba1_scan);
   m.def("attention_prepare(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, Tensor? q_norm_w, "
-        "Tensor? k_norm_w, float eps, Tensor? inv_freq, Tensor? v_first, float v_lambda, Tensor(c!) q_out, int pad=0) -> ()", &attention_prepare);
+        "Tensor? k_norm_w, float eps, Tensor? inv_freq, Tensor? v_first, float v_lambda, Tensor(c!) q_out, int pad=0, Tensor? v_inv_freq=None, "
+        "bool v_interleaved=False) -> ()", &attention_prepare);
   m.def("sigmoid_gate(Tensor o, Tensor gate, int Dv, float out_scale, Tensor(a!) out) -> ()", &sigmoid_gate);
-  m.def("activation(Tensor x, int act, Tensor(a!) out) -> ()", &activation);
+  m.def("activation(Tensor x, int act, Tensor(a!) out, Tensor? mul=None) -> ()", &activation);
   m.def("qk_norm_cache_write(Tensor qkv, int H, int G, int D, int Dv, Tensor positions, float eps, float temp_coef, int temp_every, "
         "Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor loc, bool normalise, Tensor(c!) q_out, int pad=0) -> ()", &qk_norm_cache_write);
   m.def("window_attention(Tensor q, Tensor k_cache, Tensor v_cache, int G, int Dv, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
@@ -1021,7 +1151,17 @@ TORCH_LIBRARY(sglb, m) {
         "Tensor req_slots, Tensor seq_lens, Tensor? cu_q, Tensor? gate_raw, Tensor? norm_w, float eps, bool gate_silu, bool per_channel, Tensor(b!) out) -> ()",
         &gated_delta_rule);
   m.def("latent_attention(Tensor q, Tensor cache, int rank, Tensor page_table, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, int max_q_len, "
-        "int max_kv_len, int page_size, float scale, int window, Tensor? sinks, Tensor(a!) out) -> ()", &latent_attention);
+        "int max_kv_len, int page_size, float scale, int window, Tensor? sinks, Tensor(a!) out, int v_rank=0) -> ()", &latent_attention);
+  m.def("latent_prepare(Tensor x, int q_rank, Tensor? q_norm_w, int rank, int rot_dim, Tensor kv_norm_w, float eps, Tensor positions, Tensor? inv_freq, "
+        "float mult, Tensor(a!) cache, Tensor loc, Tensor(b!)? cq) -> ()", &latent_prepare);
+  m.def("latent_query(Tensor q, Tensor q_abs, int dim, int rot_dim, Tensor positions, Tensor? inv_freq, float mult, Tensor(a!) out) -> ()", &latent_query);
+  m.def("rotate_heads(Tensor o, Tensor positions, Tensor inv_freq, int Dv, bool interleaved, bool inverse, Tensor? lse, Tensor? sinks, Tensor(a!) out) -> ()",
+        &rotate_heads);
+  m.def("parallel_add_rmsnorm_f32(Tensor(a!) residual, Tensor? d1, Tensor? d2, Tensor? d3, Tensor w1, Tensor? w2, Tensor(b!) out1, Tensor(c!)? out2, float eps, "
+        "bool zero_centred) -> ()", &parallel_add_rmsnorm_f32);
+  m.def("mlstm_prepare(Tensor proj, Tensor gates_raw, int H, int D, int Dv, float cap, Tensor(a!) mstate, Tensor req_slots, Tensor seq_lens, Tensor? cu_q, "
+        "Tensor(b!) u, Tensor(c!) gates) -> ()", &mlstm_prepare);
+  m.def("mlstm_readout(Tensor y, Tensor gates, int H, int Dv, Tensor norm_w, float eps, Tensor? gate, Tensor(a!) out) -> ()", &mlstm_readout);
   m.def("gated_delta_update(Tensor(a!) state, Tensor req_slots, Tensor u, Tensor g, Tensor beta, int Hk, Tensor(b!) out) -> ()", &gated_delta_update);
   m.def("causal_conv1d(Tensor x, Tensor w, Tensor? bias, Tensor(a!) conv_state, Tensor? cu_q, Tensor req_slots, Tensor seq_lens, int max_q_len, "
         "bool silu, Tensor(b!) u) -> ()", &causal_conv1d);

@@ -121,18 +121,26 @@ void sigmoid_gate(const void* o, int head_stride, const void* gate, int ldg, boo
                   cudaStream_t stream);
 void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, const void* q_norm_w, const void* k_norm_w,
                        float eps, const float* inv_freq, int half, const void* v_first, int ldvf, float lam, void* kc, void* vc, size_t ldc, const int* loc,
-                       void* q_out, int pad, cudaStream_t stream);
+                       void* q_out, int pad, const float* v_inv_freq, bool v_interleaved, cudaStream_t stream);
+void rotate_heads(const void* o, int head_stride, bool bf16, const int* positions, const float* inv_freq, int T, int H, int Dv, bool interleaved, bool inverse,
+                  const float* lse, const float* sinks, void* out, cudaStream_t stream);
 void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream);
 // mamba.cu (ragged Mamba-2 recurrence), residual_f32.cu (sandwich norms), elementwise.cu (bigram embedding), moe.cu (identity / shared experts)
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
                  const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
-                 const float* decay, cudaStream_t stream);
+                 const float* decay, const float* gates, int gstride, cudaStream_t stream);
+void mlstm_prepare(const void* proj, int ld, bool bf16, const float* raw, int T, int B, int H, int D, int Dv, float cap, float* mstate, const int* req_slots,
+                   const int* seq_lens, const int* cu_q, float* u, float* gates, cudaStream_t stream);
+void mlstm_readout(const float* y, const float* gates, int T, int H, int Dv, const void* w, float eps, const void* gate, int ldg, void* out, bool out_bf16,
+                   cudaStream_t stream);
 void mamba1_scan(const float* u, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log, const void* Bm, const void* Cm, int ldbc, bool bc_bf16,
                  const float* D, const void* z, int ldz, bool z_bf16, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int C,
                  int N, void* out, bool out_bf16, cudaStream_t stream);
-void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, cudaStream_t stream);
+void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, const void* mul, int ldm, cudaStream_t stream);
 void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf16, const void* post_w, const void* w, void* out, bool out_bf16, int T,
                               int H, float eps, bool zero_centred, int post_w_stride, int w_stride, cudaStream_t stream);
+void parallel_add_rmsnorm_f32(float* residual, const void* d1, const void* d2, bool delta_bf16, const float* d3, const void* w1, const void* w2, void* out1,
+                              void* out2, bool out_bf16, int T, int H, float eps, bool zero_centred, cudaStream_t stream);
 void grouped_rmsnorm(const float* x, const void* w, void* out, bool out_bf16, int T, int C, int groups, float eps, const void* gate, int ldg, int ldo,
                      float out_scale, cudaStream_t stream);
 void bigram_embedding(const void* embed, const void* bigram, bool bf16, const int* ids, int* prev_tokens, const int* cu_q, const int* req_slots,
@@ -145,7 +153,11 @@ void moe_identity_shared_combine(void* y, const void* h, const float* ident, con
 // latent_attention.cu
 void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
                       const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int max_kv_len, int H, float scale,
-                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, cudaStream_t stream);
+                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, int v_rank, cudaStream_t stream);
+void latent_prepare(const void* x, int ld, bool bf16, int T, int Rq, const void* wq, int R, int Dr, const void* wk, float eps, const int* positions,
+                    const float* inv_freq, float mult, void* cache, size_t ldc, const int* loc, void* cq, cudaStream_t stream);
+void latent_query(const void* q, bool bf16, const float* q_abs, int T, int H, int D, int Dr, int R, const int* positions, const float* inv_freq, float mult,
+                  float* out, cudaStream_t stream);
 void greedy_shard(const void* logits, bool bf16, int B, int stride, int v_valid, int v_offset, int rank, int tp, int b_pad, void* buf,
                   cudaStream_t stream);
 void greedy_merge(const void* buf, int tp, int b_pad, int B, const int* out_slots, int* next_token_buf, int* out_tokens, cudaStream_t stream);

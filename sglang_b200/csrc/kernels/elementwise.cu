@@ -455,9 +455,11 @@ void bigram_embedding(const void* embed, const void* bigram, bool bf16, const in
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
-// ---------------------------------------------------------------- act(x) element-wise, [T, n] rows of ldx elements -> contiguous [T, n]
+// ---------------------------------------------------------------- act(x) element-wise, [T, n] rows of ldx elements -> contiguous [T, n];
+// with ``mul`` ([T, n] rows of ldm elements, x's type): act(x) * mul, the gated feed-forward's middle
 template <typename TI, typename TO, int ACT>  // 0 silu, 2 gelu(tanh)
-__global__ void __launch_bounds__(256) activation_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n) {
+__global__ void __launch_bounds__(256) activation_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n,
+                                                         const TI* __restrict__ mul, int ldm) {
   const size_t total = (size_t)T * n;
   for (size_t idx = blockIdx.x * (size_t)256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
     const size_t t = idx / n;
@@ -467,13 +469,17 @@ __global__ void __launch_bounds__(256) activation_kernel(const TI* __restrict__ 
     float a;
     if (ACT == 0) a = v / (1.f + expf(-v));
     else { const float c = 0.7978845608028654f * (v + 0.044715f * v * v * v); a = 0.5f * v * (1.f + tanhf(c)); }
+    if (mul) {
+      if constexpr (sizeof(TI) == 2) a *= __bfloat162float(mul[t * ldm + i]); else a *= mul[t * ldm + i];
+    }
     if constexpr (sizeof(TO) == 2) out[idx] = __float2bfloat16(a); else out[idx] = a;
   }
 }
 
 // eight elements per thread, 16-byte accesses (n and ldx multiples of 8, 16-byte aligned bases)
 template <typename TI, typename TO, int ACT>
-__global__ void __launch_bounds__(256) activation_vec8_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n8) {
+__global__ void __launch_bounds__(256) activation_vec8_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, int T, int n8,
+                                                              const TI* __restrict__ mul, int ldm) {
   const size_t total = (size_t)T * n8;
   for (size_t idx = blockIdx.x * (size_t)256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
     const size_t t = idx / n8;
@@ -492,6 +498,16 @@ __global__ void __launch_bounds__(256) activation_vec8_kernel(const TI* __restri
       if (ACT == 0) v[k] = v[k] / (1.f + expf(-v[k]));
       else { const float c = 0.7978845608028654f * (v[k] + 0.044715f * v[k] * v[k] * v[k]); v[k] = 0.5f * v[k] * (1.f + tanhf(c)); }
     }
+    if (mul) {
+      if constexpr (sizeof(TI) == 2) {
+        const U4 a = ld128(mul + t * ldm + i);
+        v[0] *= bf16_lo(a.x); v[1] *= bf16_hi(a.x); v[2] *= bf16_lo(a.y); v[3] *= bf16_hi(a.y);
+        v[4] *= bf16_lo(a.z); v[5] *= bf16_hi(a.z); v[6] *= bf16_lo(a.w); v[7] *= bf16_hi(a.w);
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(mul + t * ldm + i), b = *reinterpret_cast<const float4*>(mul + t * ldm + i + 4);
+        v[0] *= a.x; v[1] *= a.y; v[2] *= a.z; v[3] *= a.w; v[4] *= b.x; v[5] *= b.y; v[6] *= b.z; v[7] *= b.w;
+      }
+    }
     TO* o = out + idx * 8;
     if constexpr (sizeof(TO) == 2) {
       st128(o, U4{pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7])});
@@ -502,17 +518,17 @@ __global__ void __launch_bounds__(256) activation_vec8_kernel(const TI* __restri
   }
 }
 
-void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, cudaStream_t stream) {
+void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, int T, int n, int act, const void* mul, int ldm, cudaStream_t stream) {
   if (T <= 0 || n <= 0) return;
   using bf = __nv_bfloat16;
-  if (n % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+  if (n % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && (!mul || (ldm % 8 == 0 && ((uintptr_t)mul % 16) == 0))) {
     const size_t tv = (size_t)T * (n / 8);
     const size_t gv = (tv + 255) / 256;
     const int gridv = (int)(gv < (size_t)(148 * 16) ? gv : (size_t)(148 * 16));
 #define SGLB_ACTV(TI, TO)                                                                                                        \
   do {                                                                                                                           \
-    if (act == 0) activation_vec8_kernel<TI, TO, 0><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8);           \
-    else activation_vec8_kernel<TI, TO, 2><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8);                    \
+    if (act == 0) activation_vec8_kernel<TI, TO, 0><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8, (const TI*)mul, ldm); \
+    else activation_vec8_kernel<TI, TO, 2><<<gridv, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n / 8, (const TI*)mul, ldm); \
   } while (0)
     if (x_bf16) { if (out_bf16) SGLB_ACTV(bf, bf); else SGLB_ACTV(bf, float); }
     else { if (out_bf16) SGLB_ACTV(float, bf); else SGLB_ACTV(float, float); }
@@ -525,8 +541,8 @@ void activation(const void* x, int ldx, bool x_bf16, void* out, bool out_bf16, i
   const int grid = (int)(gq < (size_t)(148 * 16) ? gq : (size_t)(148 * 16));
 #define SGLB_ACT(TI, TO)                                                                                                   \
   do {                                                                                                                     \
-    if (act == 0) activation_kernel<TI, TO, 0><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n);               \
-    else activation_kernel<TI, TO, 2><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n);                        \
+    if (act == 0) activation_kernel<TI, TO, 0><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n, (const TI*)mul, ldm); \
+    else activation_kernel<TI, TO, 2><<<grid, 256, 0, stream>>>((const TI*)x, ldx, (TO*)out, T, n, (const TI*)mul, ldm); \
   } while (0)
   if (x_bf16) { if (out_bf16) SGLB_ACT(bf, bf); else SGLB_ACT(bf, float); }
   else { if (out_bf16) SGLB_ACT(float, bf); else SGLB_ACT(float, float); }

@@ -22,6 +22,9 @@ constexpr int NW = 8;            // warps per CTA
 template <typename T> __device__ __forceinline__ float ldc(const T* p);
 template <> __device__ __forceinline__ float ldc<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ldc<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stc(T* p, float v);
+template <> __device__ __forceinline__ void stc<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stc<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 
 struct LatentParams {
   const float* q; float* out;                 // [T, H, R]
@@ -30,6 +33,7 @@ struct LatentParams {
   const int* req_slots; const int* seq_lens; const int* cu_q;
   const float* sinks;
   int H, R, RP, HG, window;                    // RP: row stride of the key tile in shared memory (R + 4 when R % 4 == 0, else R + 1)
+  int Rv;                                      // leading columns of a row that are its value (<= R; the rest only scores); out rows are Rv wide
   float scale;
   int vec8;
   int nsplit;                                  // decode only: the visible keys of a request are cut into nsplit ranges, one CTA each
@@ -50,7 +54,7 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
   const int pos0 = L - n + t0;                 // position of the CTA's first query
   const int h0 = blockIdx.z * p.HG;
   const int nh = min(p.HG, p.H - h0);
-  const int R = p.R, RP = p.RP;
+  const int R = p.R, RP = p.RP, Rv = p.Rv;
   const bool vec = (R & 3) == 0;               // 16-byte shared-memory loads of queries and latent rows
   const bool vec8 = p.vec8 != 0;               // 16-byte global loads of cache rows (rank, row stride and base allow it)
   const int P = nq * nh;                       // (query, head) pairs of this CTA: pair = qi * nh + hi
@@ -183,11 +187,11 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
 #pragma unroll
       for (int u = 0; u < PP; ++u) sp[u * KT + lane] = pj[u];
       __syncwarp();
-      for (int c0 = 0; c0 < R; c0 += 64) {                  // two column groups per pass
+      for (int c0 = 0; c0 < Rv; c0 += 64) {                 // two column groups per pass
         float acc[PP][2];
 #pragma unroll
         for (int u = 0; u < PP; ++u) acc[u][0] = acc[u][1] = 0.f;
-        const int cc0 = min(c0 + lane, R - 1), cc1 = min(c0 + 32 + lane, R - 1);
+        const int cc0 = min(c0 + lane, Rv - 1), cc1 = min(c0 + 32 + lane, Rv - 1);
 #pragma unroll 2
         for (int j = 0; j < KT; j += 4) {
           float w[PP][4];
@@ -211,8 +215,8 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
           if (!act[u]) continue;
           float* ov = s_o + (warp + (g0 + u) * NW) * R;
           const int ca = c0 + lane, cb = c0 + 32 + lane;
-          if (ca < R) ov[ca] = ov[ca] * alpha[u] + acc[u][0];
-          if (cb < R) ov[cb] = ov[cb] * alpha[u] + acc[u][1];
+          if (ca < Rv) ov[ca] = ov[ca] * alpha[u] + acc[u][0];
+          if (cb < Rv) ov[cb] = ov[cb] * alpha[u] + acc[u][1];
         }
       }
       __syncwarp();                                          // sp is rewritten by the warp's next group of pairs
@@ -226,13 +230,13 @@ __global__ void __launch_bounds__(NW * 32) latent_attention_kernel(const LatentP
     const int qi = pr / nh, hi = pr - qi * nh;
     if (QT == 1 && p.nsplit > 1) {
       const size_t row = ((size_t)(qbase + qi) * p.nsplit + split) * p.H + h0 + hi;
-      for (int c = lane; c < R; c += 32) p.part_o[row * R + c] = s_o[pr * R + c];
+      for (int c = lane; c < Rv; c += 32) p.part_o[row * Rv + c] = s_o[pr * R + c];
       if (lane == 0) { p.part_ml[row * 2] = m_run[k]; p.part_ml[row * 2 + 1] = l_run[k]; }
       continue;
     }
     const float inv = 1.f / l_run[k];
-    float* dst = p.out + ((size_t)(qbase + t0 + qi) * p.H + h0 + hi) * R;
-    for (int c = lane; c < R; c += 32) dst[c] = s_o[pr * R + c] * inv;
+    float* dst = p.out + ((size_t)(qbase + t0 + qi) * p.H + h0 + hi) * Rv;
+    for (int c = lane; c < Rv; c += 32) dst[c] = s_o[pr * R + c] * inv;
   }
 }
 
@@ -289,7 +293,7 @@ void launch(LatentParams p, int B, int max_q_len, int max_kv_len, float* workspa
     if ((size_t)B * ns * p.H * (p.R + 2) > workspace_floats) ns = 1;
     p.nsplit = ns;
     p.part_o = workspace;
-    p.part_ml = workspace + (size_t)B * ns * p.H * p.R;
+    p.part_ml = workspace + (size_t)B * ns * p.H * p.Rv;
   }
   const size_t smem = tile + per_head * hg;
   dim3 grid(QT == 1 ? p.nsplit : (max_q_len + QT - 1) / QT, B, hgroups);
@@ -299,21 +303,108 @@ void launch(LatentParams p, int B, int max_q_len, int max_kv_len, float* workspa
   else launch_pp<TCache, QT, 1>(p, grid, smem, stream);
   if (QT == 1 && p.nsplit > 1) {
     const int rows = B * p.H;
-    latent_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, rows, p.H, p.R, p.nsplit);
+    latent_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, rows, p.H, p.Rv, p.nsplit);
     SGLB_CUDA_CHECK(cudaGetLastError());
+  }
+}
+
+
+// ---------------------------------------------------------------- what lies around the absorbed kernel when queries pass a latent and a rotary part is shared
+// latent_prepare: per token, rows of x = [query latent (Rq) | key/value latent (R) | rotary key (Dr)]:
+//   cq = query latent / rms * wq (x's type);  cache[loc, :R] = key/value latent / rms * wk;  cache[loc, R:R+Dr] = rotary key turned by
+//   position * inv_freq[m] on neighbouring pairs (2m, 2m + 1), sine and cosine times mult.  Norms, angle, sine and cosine fp32.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict__ x, int ld, int Rq, const T* __restrict__ wq, int R, int Dr,
+                                                             const T* __restrict__ wk, float eps, const int* __restrict__ positions,
+                                                             const float* __restrict__ inv_freq, float mult, T* __restrict__ cache, size_t cstride,
+                                                             const int* __restrict__ loc, T* __restrict__ cq) {
+  __shared__ float red[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const T* row = x + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = tid; i < Rq; i += 128) { const float v = ldc<T>(row + i); sq += v * v; }
+  for (int i = tid; i < R; i += 128) { const float v = ldc<T>(row + Rq + i); sk += v * v; }
+  sq = warp_sum(sq); sk = warp_sum(sk);
+  if ((tid & 31) == 0) { red[tid >> 5] = sq; red[4 + (tid >> 5)] = sk; }
+  __syncthreads();
+  const float rq = Rq > 0 ? 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)Rq + eps) : 0.f;
+  const float rk = 1.0f / sqrtf((red[4] + red[5] + red[6] + red[7]) / (float)R + eps);
+  T* crow = cache + (size_t)loc[t] * cstride;
+  for (int i = tid; i < Rq; i += 128) stc<T>(cq + (size_t)t * Rq + i, ldc<T>(row + i) * rq * ldc<T>(wq + i));
+  for (int i = tid; i < R; i += 128) stc<T>(crow + i, ldc<T>(row + Rq + i) * rk * ldc<T>(wk + i));
+  const float pos = (float)positions[t];
+  for (int m = tid; m < Dr / 2; m += 128) {
+    const float a = ldc<T>(row + Rq + R + 2 * m), b = ldc<T>(row + Rq + R + 2 * m + 1);
+    float sn = 0.f, cs = 1.f;
+    if (inv_freq) {
+      sincosf(pos * inv_freq[m], &sn, &cs);
+      sn *= mult; cs *= mult;
+    }
+    stc<T>(crow + R + 2 * m, a * cs - b * sn);
+    stc<T>(crow + R + 2 * m + 1, b * cs + a * sn);
+  }
+}
+
+// latent_query: out[t, h, :R] = q_abs[h, t, :] (the unrotated query already multiplied into the key up-projection), out[t, h, R:] = the rotary
+// columns q[t, h, D:D+Dr] turned like the key's; grid (T, H)
+template <typename T>
+__global__ void __launch_bounds__(128) latent_query_kernel(const T* __restrict__ q, const float* __restrict__ q_abs, int Tn, int H, int D, int Dr, int R,
+                                                           const int* __restrict__ positions, const float* __restrict__ inv_freq, float mult,
+                                                           float* __restrict__ out) {
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  float* dst = out + ((size_t)t * H + h) * (R + Dr);
+  const float* src = q_abs + ((size_t)h * Tn + t) * R;
+  for (int i = tid; i < R; i += 128) dst[i] = src[i];
+  const T* qr = q + ((size_t)t * H + h) * (D + Dr) + D;
+  const float pos = (float)positions[t];
+  for (int m = tid; m < Dr / 2; m += 128) {
+    const float a = ldc<T>(qr + 2 * m), b = ldc<T>(qr + 2 * m + 1);
+    float sn = 0.f, cs = 1.f;
+    if (inv_freq) {
+      sincosf(pos * inv_freq[m], &sn, &cs);
+      sn *= mult; cs *= mult;
+    }
+    dst[R + 2 * m] = a * cs - b * sn;
+    dst[R + 2 * m + 1] = b * cs + a * sn;
   }
 }
 
 }  // namespace
 
+void latent_prepare(const void* x, int ld, bool bf16, int T, int Rq, const void* wq, int R, int Dr, const void* wk, float eps, const int* positions,
+                    const float* inv_freq, float mult, void* cache, size_t ldc, const int* loc, void* cq, cudaStream_t stream) {
+  if (T <= 0) return;
+  using bf = __nv_bfloat16;
+  if (bf16)
+    latent_prepare_kernel<bf><<<T, 128, 0, stream>>>((const bf*)x, ld, Rq, (const bf*)wq, R, Dr, (const bf*)wk, eps, positions, inv_freq, mult, (bf*)cache,
+                                                     ldc, loc, (bf*)cq);
+  else
+    latent_prepare_kernel<float><<<T, 128, 0, stream>>>((const float*)x, ld, Rq, (const float*)wq, R, Dr, (const float*)wk, eps, positions, inv_freq, mult,
+                                                        (float*)cache, ldc, loc, (float*)cq);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void latent_query(const void* q, bool bf16, const float* q_abs, int T, int H, int D, int Dr, int R, const int* positions, const float* inv_freq, float mult,
+                  float* out, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return;
+  if (H > 65535) throw std::runtime_error("sglb latent_query: more than 65535 heads");
+  dim3 grid(T, H);
+  if (bf16)
+    latent_query_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, q_abs, T, H, D, Dr, R, positions, inv_freq, mult, out);
+  else
+    latent_query_kernel<float><<<grid, 128, 0, stream>>>((const float*)q, q_abs, T, H, D, Dr, R, positions, inv_freq, mult, out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
 void latent_attention(const float* q, const void* cache, bool cache_bf16, int ldc, int R, const int* page_table, int pt_stride, int page_size,
                       const int* req_slots, const int* seq_lens, const int* cu_q, int B, int max_q_len, int max_kv_len, int H, float scale,
-                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, cudaStream_t stream) {
+                      int window, const float* sinks, float* out, float* workspace, size_t workspace_floats, int v_rank, cudaStream_t stream) {
   if (B <= 0 || max_q_len <= 0) return;
+  if (v_rank <= 0 || v_rank > R) throw std::runtime_error("sglb latent_attention: the value is a leading part of the row");
   if (B > 65535) throw std::runtime_error("sglb latent_attention: more than 65535 requests in one call");
   LatentParams p;
   p.q = q; p.out = out; p.cache = cache; p.ldc = ldc; p.page_table = page_table; p.pt_stride = pt_stride; p.page_size = page_size;
-  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.RP = R + 1; p.HG = 1;
+  p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.sinks = sinks; p.H = H; p.R = R; p.RP = R + 1; p.HG = 1; p.Rv = v_rank;
   const int esz = cache_bf16 ? 2 : 4;
   p.vec8 = (R % 8 == 0 && ((size_t)ldc * esz) % 16 == 0 && ((uintptr_t)cache % 16) == 0) ? 1 : 0; p.window = window; p.scale = scale; p.nsplit = 1; p.part_o = nullptr; p.part_ml = nullptr;
   const bool decode = cu_q == nullptr || max_q_len == 1;

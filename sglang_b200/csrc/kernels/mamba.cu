@@ -260,6 +260,7 @@ struct Mamba2Params {
   const void* dt_raw; int lddt;                  // [T, >= H] (model dtype)
   const float* dt_bias; const float* A_log; const float* D;
   const float* decay;                            // non-null: step size 1 and the head's constant decay (dt_raw, dt_bias, A_log unused)
+  const float* gates; int gstride;               // non-null: [T, H, gstride] with every token's decay at [0] and step at [1] (likewise)
   float* state;                                  // [slots, H, N, P]
   const int* req_slots; const int* seq_lens; const int* cu_q;
   float* out;                                    // [T, H*P]
@@ -311,16 +312,17 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
     for (int idx = tid; idx < 2 * stage; idx += 128) sm[idx] = 0.f;
     __syncthreads();
   }
-  const float a_exp = p.decay ? 0.f : expf(p.A_log[h]);
+  const bool fixed = p.decay || p.gates;
+  const float a_exp = fixed ? 0.f : expf(p.A_log[h]);
   const float dskip = p.D ? p.D[h] : 0.f;
-  const float dtb = p.decay ? 0.f : p.dt_bias[h];
+  const float dtb = fixed ? 0.f : p.dt_bias[h];
   const float fixed_decay = p.decay ? p.decay[h] : 0.f;
   const TZ* zg = reinterpret_cast<const TZ*>(p.z);
   const TZ* dg = reinterpret_cast<const TZ*>(p.dt_raw);
   const int inner = H * P;
   const int pw = min(PC, P - pc * PC);                      // live columns of this CTA
   float zr[ZR];
-  float dtr = 0.f;
+  float dtr = 0.f, dar = 0.f;
 
   auto issue = [&](int t0, float* buf) {      // start the copies of chunk [t0, t0 + TC) into buf; z and dt go to registers
     const int tc = min(TC, n - t0);
@@ -341,7 +343,13 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
       const int idx = tid + k * 128, tt = idx / PC, c = idx - tt * PC;
       zr[k] = (zg && tt < tc && c < pw) ? ld_f<TZ>(zg + (size_t)(q0 + t0 + tt) * p.ldz + h * P + pc * PC + c) : 0.f;
     }
-    if (dg && tid < tc) dtr = ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h);
+    if (p.gates) {
+      if (tid < tc) {
+        const float* gt = p.gates + ((size_t)(q0 + t0 + tid) * H + h) * p.gstride;
+        dar = gt[0];
+        dtr = gt[1];
+      }
+    } else if (dg && tid < tc) dtr = ld_f<TZ>(dg + (size_t)(q0 + t0 + tid) * p.lddt + h);
   };
   auto land = [&](int t0, float* buf) {       // finish what issue() started
     const int tc = min(TC, n - t0);
@@ -352,9 +360,9 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const Mamba2Params p) 
       if (idx < TC * PC) sZ[idx] = zr[k];
     }
     if (tid < tc) {
-      const float dt = p.decay ? 1.f : m2_softplus(dtr + dtb);
+      const float dt = p.gates ? dtr : p.decay ? 1.f : m2_softplus(dtr + dtb);
       sDt[tid] = dt;
-      sDa[tid] = p.decay ? fixed_decay : expf(-a_exp * dt);
+      sDa[tid] = p.gates ? dar : p.decay ? fixed_decay : expf(-a_exp * dt);
     }
     m2_cp_wait();
   };
@@ -468,16 +476,142 @@ void dispatch_m2(const Mamba2Params& p, int B, cudaStream_t stream) {
 
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,
                  const float* D, float* state, const int* req_slots, const int* seq_lens, const int* cu_q, int B, int H, int P, int N, int G, float* out,
-                 const float* decay, cudaStream_t stream) {
+                 const float* decay, const float* gates, int gstride, cudaStream_t stream) {
   if (B <= 0) return;
   if (N > 1024 || B > 65535 || H % G) throw std::runtime_error("sglb mamba2_scan: state size up to 1024, heads a multiple of groups");
-  if (!decay && (!dt_raw || !dt_bias || !A_log)) throw std::runtime_error("sglb mamba2_scan: step-size inputs or a constant decay");
+  if (!decay && !gates && (!dt_raw || !dt_bias || !A_log)) throw std::runtime_error("sglb mamba2_scan: step-size inputs, a constant decay or per-token gates");
   Mamba2Params p;
-  p.decay = decay;
+  p.decay = decay; p.gates = gates; p.gstride = gstride;
   p.u = u; p.ldu = ldu; p.z = z; p.ldz = ldz; p.dt_raw = dt_raw; p.lddt = lddt; p.dt_bias = dt_bias; p.A_log = A_log; p.D = D; p.state = state;
   p.req_slots = req_slots; p.seq_lens = seq_lens; p.cu_q = cu_q; p.out = out; p.H = H; p.P = P; p.N = N; p.G = G; p.pchunks = 1;
   if (bf16) dispatch_m2<__nv_bfloat16>(p, B, stream);
   else dispatch_m2<float>(p, B, stream);
+}
+
+// ---------------------------------------------------------------- matrix memory with exponential gates and a running maximum (mLSTM): what surrounds the scan
+//   i = cap tanh(raw_i / cap);  f = logsigmoid(cap tanh(raw_f / cap));  m_t = max(f + m_(t-1), i), m = 0 at the start of a sequence;
+//   decay_t = exp(f + m_(t-1) - m_t), step_t = exp(i - m_t), floor_t = exp(-m_t).
+// With those the memory S_t = decay_t S_(t-1) + step_t k v^T and its normaliser n_t (the same recurrence on a value that is always 1) run on
+// mamba2_scan(gates): x = [v | 1] per head, B = k, C = q / sqrt(D).
+// mlstm_prepare, one launch with two kinds of CTA: the first T write a token's [x | B | C] row in fp32; the others hold four warps, a warp per
+// (request, head), which walks m through the request's tokens 32 at a time (gate activations lane-parallel, the max-chain by shuffles, the three
+// exponentials lane-parallel again) and leaves m in mstate [slots, H].  Everything fp32.
+// mlstm_readout: o = y[:Dv] / (max(|y[Dv]|, floor) + 1e-6) per head, divided by its root mean square, times weight, times sigmoid(gate); a warp
+// per (token, head).
+namespace {
+
+template <typename T> __device__ __forceinline__ float ml_ld(const T* p);
+template <> __device__ __forceinline__ float ml_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ml_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void ml_st(T* p, float v);
+template <> __device__ __forceinline__ void ml_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void ml_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(128) mlstm_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ raw, int H, int D, int Dv, float cap,
+                                                            float* __restrict__ mstate, const int* __restrict__ req_slots, const int* __restrict__ seq_lens,
+                                                            const int* __restrict__ cu_q, int Tn, int B, float* __restrict__ u, float* __restrict__ gates) {
+  const int tid = threadIdx.x;
+  if ((int)blockIdx.x < Tn) {
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * ld;
+    const int nk = H * D, P = Dv + 1, nx = H * P;
+    float* dst = u + (size_t)t * (nx + 2 * nk);
+    for (int idx = tid; idx < nx; idx += 128) {
+      const int h = idx / P, c = idx - h * P;
+      dst[idx] = c < Dv ? ml_ld<T>(row + 2 * nk + h * Dv + c) : 1.f;
+    }
+    const float qs = 1.0f / sqrtf((float)D);
+    for (int idx = tid; idx < nk; idx += 128) {
+      dst[nx + idx] = ml_ld<T>(row + nk + idx);
+      dst[nx + nk + idx] = ml_ld<T>(row + idx) * qs;
+    }
+    return;
+  }
+  const int w = ((int)blockIdx.x - Tn) * 4 + (tid >> 5), lane = tid & 31;
+  if (w >= B * H) return;
+  const int b = w / H, h = w - b * H;
+  const int q0 = cu_q ? cu_q[b] : b;
+  const int n = cu_q ? cu_q[b + 1] - q0 : 1;
+  if (n <= 0) return;
+  float* ms = mstate + (size_t)req_slots[b] * H + h;
+  float m = seq_lens[b] - n == 0 ? 0.f : *ms;
+  for (int t0 = 0; t0 < n; t0 += 32) {
+    const int tt = t0 + lane;
+    float ig = 0.f, fg = 0.f;
+    if (tt < n) {
+      const float* r = raw + (size_t)(q0 + tt) * 2 * H;
+      float ri = r[h], rf = r[H + h];
+      if (cap > 0.f) { ri = cap * tanhf(ri / cap); rf = cap * tanhf(rf / cap); }
+      ig = ri;
+      fg = fminf(rf, 0.f) - log1pf(expf(-fabsf(rf)));
+    }
+    float m_prev = 0.f, m_new = 0.f;
+    const int cnt = min(32, n - t0);
+    for (int j = 0; j < cnt; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, fg, j), ij = __shfl_sync(0xffffffffu, ig, j);
+      const float mn = fmaxf(fj + m, ij);
+      if (lane == j) { m_prev = m; m_new = mn; }
+      m = mn;
+    }
+    if (tt < n) {
+      float* g = gates + ((size_t)(q0 + tt) * H + h) * 3;
+      g[0] = expf(fg + m_prev - m_new);
+      g[1] = expf(ig - m_new);
+      g[2] = expf(-m_new);
+    }
+  }
+  if (lane == 0) *ms = m;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128) mlstm_readout_kernel(const float* __restrict__ y, const float* __restrict__ gates, int rows, int H, int Dv,
+                                                            const TO* __restrict__ w, float eps, const TO* __restrict__ gate, int ldg, TO* __restrict__ out) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;          // row = t * H + h
+  if (row >= rows) return;
+  const int t = row / H, h = row - t * H;
+  const float* yy = y + (size_t)row * (Dv + 1);
+  const float den = fmaxf(fabsf(yy[Dv]), gates[(size_t)row * 3 + 2]) + 1e-6f;
+  float ss = 0.f;
+  for (int c = lane; c < Dv; c += 32) {
+    const float o = yy[c] / den;
+    ss += o * o;
+  }
+  const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+  const TO* wr = w + (size_t)h * Dv;
+  const TO* gr = gate ? gate + (size_t)t * ldg + (size_t)h * Dv : nullptr;
+  TO* dst = out + (size_t)row * Dv;
+  for (int c = lane; c < Dv; c += 32) {
+    float v = yy[c] / den * rs * ml_ld<TO>(wr + c);
+    if (gr) v *= 1.f / (1.f + expf(-ml_ld<TO>(gr + c)));
+    ml_st<TO>(dst + c, v);
+  }
+}
+
+}  // namespace
+
+void mlstm_prepare(const void* proj, int ld, bool bf16, const float* raw, int T, int B, int H, int D, int Dv, float cap, float* mstate, const int* req_slots,
+                   const int* seq_lens, const int* cu_q, float* u, float* gates, cudaStream_t stream) {
+  if (T <= 0 || B <= 0) return;
+  const int grid = T + (B * H + 3) / 4;
+  if (bf16)
+    mlstm_prepare_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)proj, ld, raw, H, D, Dv, cap, mstate, req_slots, seq_lens, cu_q, T, B,
+                                                                  u, gates);
+  else
+    mlstm_prepare_kernel<float><<<grid, 128, 0, stream>>>((const float*)proj, ld, raw, H, D, Dv, cap, mstate, req_slots, seq_lens, cu_q, T, B, u, gates);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void mlstm_readout(const float* y, const float* gates, int T, int H, int Dv, const void* w, float eps, const void* gate, int ldg, void* out, bool out_bf16,
+                   cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return;
+  const int rows = T * H;
+  if (out_bf16)
+    mlstm_readout_kernel<__nv_bfloat16><<<(rows + 3) / 4, 128, 0, stream>>>(y, gates, rows, H, Dv, (const __nv_bfloat16*)w, eps, (const __nv_bfloat16*)gate,
+                                                                            ldg, (__nv_bfloat16*)out);
+  else
+    mlstm_readout_kernel<float><<<(rows + 3) / 4, 128, 0, stream>>>(y, gates, rows, H, Dv, (const float*)w, eps, (const float*)gate, ldg, (float*)out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
 // ---------------------------------------------------------------- Mamba-1 selective scan over a ragged batch

@@ -120,6 +120,103 @@ __global__ void __launch_bounds__(256) postnorm_add_rmsnorm_f32_kernel(float* __
   for (int i = threadIdx.x; i < H; i += 256) stf<TO>(o + i, r[i] * rs * (one + ldf<TO>(w + i * ws)));      // each thread re-reads what it wrote
 }
 
+
+// residual += d1 + d2 + d3 (each optional; d1 / d2 in the model dtype, d3 fp32; the deltas are summed first);  out1 = rmsnorm(residual) * (one + w1),
+// out2 likewise under w2 (optional): the residual update of a block whose two branches read the same input, with both pre-norms of the next
+// block, in one pass over the row.  Four columns per access; a thread keeps up to four accesses of the row in registers.
+template <typename T> __device__ __forceinline__ float4 ld4f(const T* p);
+template <> __device__ __forceinline__ float4 ld4f<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4f<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+}
+template <typename T> __device__ __forceinline__ void st4f(T* p, float4 v);
+template <> __device__ __forceinline__ void st4f<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4f<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+template <typename TD, typename TO, int VEC>
+__global__ void __launch_bounds__(256) parallel_add_rmsnorm_f32_kernel(float* __restrict__ res, const TD* __restrict__ d1, const TD* __restrict__ d2,
+                                                                       const float* __restrict__ d3, const TO* __restrict__ w1, const TO* __restrict__ w2,
+                                                                       TO* __restrict__ out1, TO* __restrict__ out2, int H, float eps, float one) {
+  __shared__ float red[8];
+  const size_t off = (size_t)blockIdx.x * H;
+  float* r = res + off;
+  const bool any = d1 || d2 || d3;
+  float ss = 0.f;
+  if constexpr (VEC == 4) {
+    constexpr int KEEP = 4;
+    float4 keep[KEEP];
+    const int n4 = H >> 2;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int i = (threadIdx.x + k * 256) * 4;
+      keep[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < H) {
+        float4 v = *reinterpret_cast<const float4*>(r + i);
+        if (any) {
+          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (d1) { const float4 t = ld4f<TD>(d1 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+          if (d2) { const float4 t = ld4f<TD>(d2 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+          if (d3) { const float4 t = *reinterpret_cast<const float4*>(d3 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+          *reinterpret_cast<float4*>(r + i) = v;
+        }
+        keep[k] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    }
+    for (int c = threadIdx.x + KEEP * 256; c < n4; c += 256) {          // rows wider than 4096: the rest is read again below
+      const int i = c * 4;
+      float4 v = *reinterpret_cast<const float4*>(r + i);
+      if (any) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d1) { const float4 t = ld4f<TD>(d1 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+        if (d2) { const float4 t = ld4f<TD>(d2 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+        if (d3) { const float4 t = *reinterpret_cast<const float4*>(d3 + off + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        *reinterpret_cast<float4*>(r + i) = v;
+      }
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)H + eps);
+    auto emit = [&](int i, float4 v) {
+      const float4 a = ld4f<TO>(w1 + i);
+      st4f<TO>(out1 + off + i, make_float4(v.x * rs * (one + a.x), v.y * rs * (one + a.y), v.z * rs * (one + a.z), v.w * rs * (one + a.w)));
+      if (out2) {
+        const float4 b = ld4f<TO>(w2 + i);
+        st4f<TO>(out2 + off + i, make_float4(v.x * rs * (one + b.x), v.y * rs * (one + b.y), v.z * rs * (one + b.z), v.w * rs * (one + b.w)));
+      }
+    };
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int i = (threadIdx.x + k * 256) * 4;
+      if (i < H) emit(i, keep[k]);
+    }
+    for (int c = threadIdx.x + KEEP * 256; c < n4; c += 256) emit(c * 4, *reinterpret_cast<const float4*>(r + c * 4));      // each thread re-reads what it wrote
+  } else {
+    for (int i = threadIdx.x; i < H; i += 256) {
+      float v = r[i];
+      if (any) {
+        float d = 0.f;
+        if (d1) d += ldf<TD>(d1 + off + i);
+        if (d2) d += ldf<TD>(d2 + off + i);
+        if (d3) d += d3[off + i];
+        v += d;
+        r[i] = v;
+      }
+      ss += v * v;
+    }
+    const float rs = 1.0f / sqrtf(block_sum_256(ss, red) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += 256) {          // each thread re-reads exactly the elements it wrote
+      const float y = r[i] * rs;
+      stf<TO>(out1 + off + i, y * (one + ldf<TO>(w1 + i)));
+      if (out2) stf<TO>(out2 + off + i, y * (one + ldf<TO>(w2 + i)));
+    }
+  }
+}
+
 // x fp32 [T, C] in ``groups`` equal parts: part / sqrt(mean(part^2) + eps) * w [* sigmoid(gate)] * out_scale; grid (T, groups); gate and out are
 // rows of ldg / ldo elements
 template <typename TO>
@@ -188,6 +285,28 @@ void postnorm_add_rmsnorm_f32(float* residual, const void* delta, bool delta_bf1
       postnorm_add_rmsnorm_f32_kernel<float, float><<<T, 256, 0, stream>>>(residual, (const float*)delta, (const float*)post_w, (const float*)w,
                                                                            (float*)out, H, eps, one, wsp, ws);
   }
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void parallel_add_rmsnorm_f32(float* residual, const void* d1, const void* d2, bool delta_bf16, const float* d3, const void* w1, const void* w2, void* out1,
+                              void* out2, bool out_bf16, int T, int H, float eps, bool zero_centred, cudaStream_t stream) {
+  if (T <= 0) return;
+  using bf = __nv_bfloat16;
+  const float one = zero_centred ? 1.f : 0.f;
+  auto al = [](const void* p) { return p == nullptr || ((uintptr_t)p % 16) == 0; };
+  const bool vec = H % 4 == 0 && al(residual) && al(d1) && al(d2) && al(d3) && al(w1) && al(w2) && al(out1) && al(out2);
+#define SGLB_PAR(TD, TO)                                                                                                                         \
+  do {                                                                                                                                           \
+    if (vec)                                                                                                                                     \
+      parallel_add_rmsnorm_f32_kernel<TD, TO, 4><<<T, 256, 0, stream>>>(residual, (const TD*)d1, (const TD*)d2, d3, (const TO*)w1, (const TO*)w2, \
+                                                                        (TO*)out1, (TO*)out2, H, eps, one);                                     \
+    else                                                                                                                                         \
+      parallel_add_rmsnorm_f32_kernel<TD, TO, 1><<<T, 256, 0, stream>>>(residual, (const TD*)d1, (const TD*)d2, d3, (const TO*)w1, (const TO*)w2, \
+                                                                        (TO*)out1, (TO*)out2, H, eps, one);                                     \
+  } while (0)
+  if (out_bf16) { if (delta_bf16) SGLB_PAR(bf, bf); else SGLB_PAR(float, bf); }
+  else { if (delta_bf16) SGLB_PAR(bf, float); else SGLB_PAR(float, float); }
+#undef SGLB_PAR
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 

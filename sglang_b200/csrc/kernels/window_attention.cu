@@ -341,6 +341,29 @@ __global__ void __launch_bounds__(128) sigmoid_gate_kernel(const T* __restrict__
   }
 }
 
+// out[t, h * Dv + c] = the head o[t, h, :Dv] (rows of hs elements) times sigmoid(lse[t, h] - sink[h]) (lse null: times 1), turned over its whole
+// width by -+ position * inv_freq[m]: pair m = columns (m, m + Dv/2) or, inter, (2m, 2m + 1).  Angle, sine and cosine fp32.
+template <typename T>
+__global__ void __launch_bounds__(128) rotate_heads_kernel(const T* __restrict__ o, int hs, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                                           int rows, int H, int Dv, int inter, float sign, const float* __restrict__ lse,
+                                                           const float* __restrict__ sinks, T* __restrict__ out) {
+  const int hv = Dv >> 1;
+  const size_t idx = (size_t)blockIdx.x * 128 + threadIdx.x;          // one thread per (token, head, pair)
+  if (idx >= (size_t)rows * hv) return;
+  const int row = (int)(idx / hv), m = (int)(idx - (size_t)row * hv);
+  const int t = row / H;
+  const float gte = lse ? 1.f / (1.f + expf(sinks[row - t * H] - lse[row])) : 1.f;
+  const T* src = o + (size_t)row * hs;
+  T* dst = out + (size_t)row * Dv;
+  const int ia = inter ? 2 * m : m, ib = inter ? 2 * m + 1 : m + hv;
+  const float a = wa_ld<T>(src + ia) * gte, b = wa_ld<T>(src + ib) * gte;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[m], &sn, &cs);
+  sn *= sign;
+  wa_st<T>(dst + ia, a * cs - b * sn);
+  wa_st<T>(dst + ib, b * cs + a * sn);
+}
+
 struct PrepParams {
   const void* qkv; int ld;                     // rows [q (H*D) | k (G*D) | v (G*Dv) | ...]
   int H, G, D, Dv;
@@ -348,6 +371,7 @@ struct PrepParams {
   const void* qw; const void* kw; float eps;   // projection-wide RMS norm weights (null: no norm)
   const float* inv_freq; int half;             // rotary frequencies (null: no rotation); pairs (i, i + half), i < half
   const void* v_first; int ldvf; float lam;    // values to blend with (null: none)
+  const float* v_inv_freq; int v_inter;        // values rotated over their whole head (null: no): pairs (m, m + Dv/2) or, v_inter, (2m, 2m + 1)
   void* kc; void* vc; size_t ldc; const int* loc;
   void* q_out; int Dq, hsk, hsv;               // head strides of q, key rows, value rows (>= D, D, Dv: zero padding behind the values)
 };
@@ -403,12 +427,24 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(const PrepParams
   }
   const T* vs = row + nq + nk;
   const T* vf = p.v_first ? reinterpret_cast<const T*>(p.v_first) + (size_t)t * p.ldvf : nullptr;
+  const int hv = p.Dv / 2;
   for (int idx = tid; idx < p.G * p.hsv; idx += 128) {
     const int gh = idx / p.hsv, c = idx - gh * p.hsv;
     float v = 0.f;
     if (c < p.Dv) {
-      v = wa_ld<T>(vs + gh * p.Dv + c);
-      if (vf) v = (1.f - p.lam) * v + p.lam * wa_ld<T>(vf + gh * p.Dv + c);
+      auto val = [&](int cc) {
+        const float x = wa_ld<T>(vs + gh * p.Dv + cc);
+        return vf ? (1.f - p.lam) * x + p.lam * wa_ld<T>(vf + gh * p.Dv + cc) : x;
+      };
+      v = val(c);
+      if (p.v_inv_freq) {
+        const bool first = p.v_inter ? (c & 1) == 0 : c < hv;
+        const int m = p.v_inter ? c >> 1 : (first ? c : c - hv);
+        const float other = val(p.v_inter ? (c ^ 1) : (first ? c + hv : c - hv));
+        float sn, cs;
+        sincosf(pos * p.v_inv_freq[m], &sn, &cs);
+        v = first ? v * cs - other * sn : v * cs + other * sn;
+      }
     }
     wa_st<T>(vo + idx, v);
   }
@@ -490,11 +526,29 @@ __global__ void __launch_bounds__(128) attention_prepare_vec_kernel(const PrepPa
     const int gh = idx / hv2, c = 2 * (idx - gh * hv2);
     float2 v = make_float2(0.f, 0.f);
     if (c < p.Dv) {
-      v = wa_ld2(vs + gh * p.Dv + c);
-      if (vf) {
-        const float2 f = wa_ld2(vf + gh * p.Dv + c);
-        v.x = (1.f - p.lam) * v.x + p.lam * f.x;
-        v.y = (1.f - p.lam) * v.y + p.lam * f.y;
+      auto val2 = [&](int cc) {
+        float2 x = wa_ld2(vs + gh * p.Dv + cc);
+        if (vf) {
+          const float2 f = wa_ld2(vf + gh * p.Dv + cc);
+          x.x = (1.f - p.lam) * x.x + p.lam * f.x;
+          x.y = (1.f - p.lam) * x.y + p.lam * f.y;
+        }
+        return x;
+      };
+      v = val2(c);
+      if (p.v_inv_freq && p.v_inter) {            // (c, c + 1) is pair c / 2
+        float sn, cs;
+        sincosf(pos * p.v_inv_freq[c >> 1], &sn, &cs);
+        v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
+      } else if (p.v_inv_freq) {                  // columns c, c + 1 belong to two pairs whose partners lie half a head away (Dv / 2 even)
+        const int hv = p.Dv / 2;
+        const bool first = c < hv;
+        const int m = first ? c : c - hv;
+        const float2 o = val2(first ? c + hv : c - hv);
+        float s0, c0, s1, c1;
+        sincosf(pos * p.v_inv_freq[m], &s0, &c0);
+        sincosf(pos * p.v_inv_freq[m + 1], &s1, &c1);
+        v = first ? make_float2(v.x * c0 - o.x * s0, v.y * c1 - o.y * s1) : make_float2(v.x * c0 + o.x * s0, v.y * c1 + o.y * s1);
       }
     }
     wa_st2(vo + (size_t)gh * p.hsv + c, v.x, v.y);
@@ -516,16 +570,17 @@ void sigmoid_gate(const void* o, int head_stride, const void* gate, int ldg, boo
 
 void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, int D, int Dv, const int* positions, const void* q_norm_w, const void* k_norm_w,
                        float eps, const float* inv_freq, int half, const void* v_first, int ldvf, float lam, void* kc, void* vc, size_t ldc, const int* loc,
-                       void* q_out, int pad, cudaStream_t stream) {
+                       void* q_out, int pad, const float* v_inv_freq, bool v_interleaved, cudaStream_t stream) {
   if (T <= 0) return;
   PrepParams p;
+  p.v_inv_freq = v_inv_freq; p.v_inter = v_interleaved ? 1 : 0;
   p.qkv = qkv; p.ld = ld; p.H = H; p.G = G; p.D = D; p.Dv = Dv; p.positions = positions; p.qw = q_norm_w; p.kw = k_norm_w; p.eps = eps;
   p.inv_freq = inv_freq; p.half = half; p.v_first = v_first; p.ldvf = ldvf; p.lam = lam; p.kc = kc; p.vc = vc; p.ldc = ldc; p.loc = loc; p.q_out = q_out;
   p.Dq = pad > 0 ? pad : D; p.hsk = pad > 0 ? pad : D; p.hsv = pad > 0 ? pad : Dv;
   const size_t a2 = bf16 ? 4 : 8;          // bytes of a two-element access
   auto al = [&](const void* q) { return q == nullptr || ((uintptr_t)q % a2) == 0; };
   const bool vec = D % 2 == 0 && Dv % 2 == 0 && half % 2 == 0 && ld % 2 == 0 && ldc % 2 == 0 && p.Dq % 2 == 0 && p.hsk % 2 == 0 && p.hsv % 2 == 0 &&
-                   (v_first == nullptr || ldvf % 2 == 0) && al(qkv) && al(kc) && al(vc) && al(q_out) && al(v_first) && al(q_norm_w) && al(k_norm_w);
+                   (v_inv_freq == nullptr || v_interleaved || Dv % 4 == 0) && (v_first == nullptr || ldvf % 2 == 0) && al(qkv) && al(kc) && al(vc) && al(q_out) && al(v_first) && al(q_norm_w) && al(k_norm_w);
   if (vec) {
     if (bf16) attention_prepare_vec_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
     else attention_prepare_vec_kernel<float><<<T, 128, 0, stream>>>(p);
@@ -533,6 +588,20 @@ void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, 
     if (bf16) attention_prepare_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(p);
     else attention_prepare_kernel<float><<<T, 128, 0, stream>>>(p);
   }
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void rotate_heads(const void* o, int head_stride, bool bf16, const int* positions, const float* inv_freq, int T, int H, int Dv, bool interleaved, bool inverse,
+                  const float* lse, const float* sinks, void* out, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return;
+  const float sign = inverse ? -1.f : 1.f;
+  const unsigned grid = (unsigned)(((size_t)T * H * (Dv / 2) + 127) / 128);
+  if (bf16)
+    rotate_heads_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)o, head_stride, positions, inv_freq, T * H, H, Dv, interleaved ? 1 : 0, sign,
+                                                                  lse, sinks, (__nv_bfloat16*)out);
+  else
+    rotate_heads_kernel<float><<<grid, 128, 0, stream>>>((const float*)o, head_stride, positions, inv_freq, T * H, H, Dv, interleaved ? 1 : 0, sign, lse, sinks,
+                                                          (float*)out);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 

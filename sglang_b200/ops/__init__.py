@@ -776,7 +776,8 @@ def glu_activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     """[gate | up] halves -> act(gate) * up with ``silu`` or ``gelu_tanh``, fp32 math, bf16 or fp32 tensors (csrc/kernels/elementwise.cu)"""
     if _use_native(x) and x.dim() == 2 and x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float32) and x.shape[1] % 2 == 0:
         out = torch.empty(x.shape[0], x.shape[1] // 2, dtype=x.dtype, device=x.device)
-        torch.ops.sglb.glu_activation(x, {"silu": 0, "gelu_tanh": 2}[kind], out)
+        F_ = x.shape[1] // 2
+        torch.ops.sglb.activation(x[:, :F_], {"silu": 0, "gelu_tanh": 2}[kind], out, x[:, F_:])
         return out
     return torch_ref.glu_activation(x, kind)
 
