@@ -202,3 +202,167 @@ def test_mlstm_prepare_scan_readout(H, D, Dv, cap, dtype):
         o_r = torch_ref.mlstm_readout(y_r, g_r, H, Dv, nw, 1e-6, proj[:, n:n + H * Dv], dtype)
         o_g = ops.mlstm_readout(y_g, g_g, H, Dv, nw.to(DEV), 1e-6, proj.to(DEV)[:, n:n + H * Dv], dtype)
         torch.testing.assert_close(o_g.cpu().float(), o_r.float(), **_tol(dtype, f32=(1e-3, 1e-3)))
+
+
+# ------------------------------------------------------------------ a far key, a key at a page border and the sink on the kernels (both attention routes)
+def _attend_cuda(H, G, D, Dv, qkv, ps, scale, cap, dtype, tc):
+    """attention of ONE request on the kernels: preparation with rotated values, the general kernel or the tcgen05 kernels (heads laid out 128
+    wide) with cap and unit sink over a paged cache whose pages lie in reverse order, back-rotation"""
+    T = qkv.shape[0]
+    n_pages = (T + ps - 1) // ps
+    pt = torch.zeros(2, n_pages + 1, dtype=torch.int32)
+    pt[1, :n_pages] = torch.arange(n_pages, 0, -1, dtype=torch.int32) + 2
+    loc = torch.tensor([int(pt[1, t // ps]) * ps + t % ps for t in range(T)], dtype=torch.int32).to(DEV)
+    pad = 128 if tc else 0
+    width = G * (pad if pad else max(D, Dv))
+    kc, vc = torch.zeros((n_pages + 4) * ps, 1, width, dtype=dtype, device=DEV), torch.zeros((n_pages + 4) * ps, 1, width, dtype=dtype, device=DEV)
+    fv = scaled_inv_freq(Dv, 100.0).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    q = ops.attention_prepare(qkv.to(dtype).to(DEV), H, G, D, Dv, pos, kc, vc, loc, None, None, 0.0, None, None, 0.0, pad, fv, False)
+    sinks = torch.zeros(H, device=DEV)
+    slots, seq, cu, ql = _i32([1]), _i32([T]), _i32([0, T]), _i32([T])
+    if tc:
+        k4, v4 = kc.view(-1, G, 128), vc.view(-1, G, 128)
+        assert ops.tc_attention_ok(q, k4, v4, ps)
+        lse = torch.empty(T, H, dtype=torch.float32, device=DEV)
+        o = ops.paged_attention(q, k4, v4, pt.to(DEV), slots, seq, cu, ql, T, ps, scale, causal=True, logit_cap=cap, lse=lse)
+        return ops.rotate_heads(o, pos, fv, Dv, False, True, lse, sinks).view(T, H, Dv).float().cpu()
+    o = ops.window_attention(q, kc, vc, G, Dv, pt.to(DEV), slots, seq, cu, ql, T, ps, scale, cap, -1, None, sinks, D, 0)
+    return ops.rotate_heads(o.view(T, H, Dv), pos, fv, Dv, False, True).view(T, H, Dv).float().cpu()
+
+
+@pytest.mark.parametrize("tc,dtype", [(False, torch.float32), (False, torch.bfloat16), (True, torch.bfloat16)])
+def test_far_key_page_border_and_sink_on_the_kernels(tc, dtype):
+    _need()
+    import rumuvik_oracle as O
+
+    H, G, D, Dv, ps = 2, 1, 8, 6, 16
+    tol = 2e-3 if dtype == torch.float32 else 5e-2
+    for T, far in ((300, 3), (300, 15), (300, 16), (129, 127), (64, 0)):
+        g = torch.Generator().manual_seed(T + far)
+        qkv = torch.randn(T, H * D + G * D + G * Dv, generator=g) * 0.1
+        kdir = torch.randn(D, generator=g)
+        kdir = kdir / kdir.norm()
+        qkv[far, H * D:H * D + D] = 6.0 * kdir
+        qkv[T - 1, :D] = 6.0 * kdir
+        val = torch.randn(Dv, generator=g)
+        qkv[far, H * D + D:] = val
+        o = _attend_cuda(H, G, D, Dv, qkv, ps, 1.0, 0.0, dtype, tc)
+        want = O.turn(val.double()[None, None, :], [T - 1 - far], O.frequencies(100.0, Dv), "halves", back=True)[0, 0]
+        torch.testing.assert_close(o[T - 1, 0].double(), want, rtol=tol, atol=tol)
+        assert float((o[T - 1, 1].double() - want).abs().max()) > 0.1
+    # one key and the sink: the key's share of the value
+    qkv = torch.zeros(1, H * D + G * D + G * Dv)
+    qkv[0, 0], qkv[0, H * D], qkv[0, H * D + D:H * D + D + 2] = 1.0, 2.0, torch.tensor([3.0, -1.0])
+    for scale, cap in ((1.0, 0.0), (0.25, 0.0), (5.0, 3.0), (-4.0, 0.0)):
+        s = 2.0 * scale
+        if cap:
+            s = cap * np.tanh(s / cap)
+        share = np.exp(s) / (1.0 + np.exp(s))
+        o = _attend_cuda(H, G, D, Dv, qkv, ps, scale, cap, dtype, tc)
+        torch.testing.assert_close(o[0, 0, :2], torch.tensor([3.0, -1.0]) * share, rtol=tol, atol=tol * 0.1)
+
+
+# ------------------------------------------------------------------ the engine on CUDA against the oracle
+def _engine_case(tmp_path, dtype, cfg, seed, tol, gen=True):
+    from test_rumuvik import Harness, _tokens
+
+    h = Harness(tmp_path, cfg, seed=seed, slots=4, max_tokens=1024, device="cuda", dtype=dtype, page=16)
+    V = cfg["vocab"]
+    a, b, c = _tokens(150, V, 1), _tokens(41, V, 2), _tokens(3, V, 3)
+    ra, rb, rc = h.oracle(a), h.oracle(b), h.oracle(c)
+    scale = float(np.abs(ra).mean()) + 1e-6
+
+    def close(x, y):
+        if dtype == "float32":
+            err = np.abs(x - y).max(-1) / scale
+            assert float(err.max()) < tol, float(err.max())
+            return
+        # bf16: per position, the root mean square over the vocabulary of the difference against that of the logits (means taken off)
+        d, r = x - y, y - y.mean(-1, keepdims=True)
+        d = d - d.mean(-1, keepdims=True)
+        err = np.sqrt((d ** 2).mean(-1)) / np.sqrt((r ** 2).mean(-1) + 1e-12)
+        assert float(err.max()) < tol and float(err.mean()) < 0.4 * tol, (float(err.max()), float(err.mean()))
+
+    close(h.step([("a", a, range(len(a)))], ["a"]), ra)                                            # whole
+    close(h.run_cut("a2", a, [100, 2, 17]), ra)                                                    # portions, then token by token
+    out = h.step([("a", a[:90], range(90)), ("b", b[:7], range(7)), ("c", c, range(3))], ["c"])    # unequal batch
+    close(out[:90], ra[:90]); close(out[90:97], rb[:7]); close(out[97:], rc)
+    out = h.step([("a", a[90:], range(60)), ("b", b[7:8], range(1))], ["a"])
+    close(out[:60], ra[90:]); close(out[60:], rb[7:8])
+    out = h.step([("b", b[8:], range(len(b) - 8)), ("d", c, range(3))], ["b", "d"])                # "d" reuses a freed slot and pages
+    close(out[:len(b) - 8], rb[8:]); close(out[len(b) - 8:], rc)
+    if dtype == "float32" and gen:  # greedy generation through the engine's own entry point, scheduler and sampler
+        prompts = [b[:9], c]
+        outs = h.eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 6, "temperature": 0, "ignore_eos": True})
+        for pr, o in zip(prompts, outs):
+            seq = list(pr)
+            for _ in range(6):
+                seq.append(int(h.oracle(seq)[-1].argmax()))
+            assert o["output_ids"] == seq[len(pr):]
+    h.close()
+
+
+def _wide():
+    """lane-friendly sizes: bf16 attention layers with group sizes 4 and 1 take the tcgen05 kernels (heads laid out 128 wide), the layer with
+    three query heads per key head the general kernel"""
+    from test_rumuvik import L, _attn, _cfg, _dense, _lat, _ml
+
+    return _cfg([L(_ml(heads=2, dim=32, vdim=64, gate_cap=10.0), _dense(128)), L(_attn(heads=8, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=1e4, scale=0.2, softcap=20.0), _dense(64)),
+                 L(_lat(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, scale=0.15), _dense(64)),
+                 L(_attn(heads=2, kv_heads=2, dim=128, vdim=32, rot_dims=128, base=50.0, scale=0.1, softcap=0), None),
+                 L(_attn(heads=6, kv_heads=2, dim=32, vdim=48, rot_dims=8, scale=0.25), _dense(32))], width=128, vocab=256, loop=(1, 4, 2), scale=4.0)
+
+
+def test_engine_on_cuda_fp32(tmp_path):
+    from test_rumuvik import MIXED
+
+    _need()
+    _engine_case(tmp_path, "float32", MIXED, 1, 3e-4)
+
+
+def test_engine_on_cuda_bf16(tmp_path):
+    from test_rumuvik import MIXED
+
+    _need()
+    _engine_case(tmp_path, "bfloat16", MIXED, 2, 0.12)
+
+
+def test_engine_on_cuda_lane_friendly_sizes_fp32(tmp_path):
+    _need()
+    _engine_case(tmp_path, "float32", _wide(), 3, 3e-4)
+
+
+def test_engine_on_cuda_lane_friendly_sizes_bf16(tmp_path):
+    _need()
+    _engine_case(tmp_path, "bfloat16", _wide(), 4, 0.12)
+
+
+def test_tensor_core_route_agrees_with_the_general_kernel(tmp_path, monkeypatch):
+    """the same bf16 model with and without the tcgen05 route: both within the bf16 tolerance of the oracle (the route is taken: its layers are padded)"""
+    from sglang_b200.layers.gated_attention import GatedAttention
+    from test_rumuvik import Harness
+
+    _need()
+    h = Harness(tmp_path, _wide(), seed=5, slots=2, max_tokens=512, device="cuda", dtype="bfloat16", page=16)
+    pads = [b.mix.pad for b in h.model.model.all_layers if b.kind == "attention"]
+    h.close()
+    assert pads == [128, 128, 0]
+    monkeypatch.setattr(GatedAttention, "tc_route", False)
+    _engine_case(tmp_path / "general", "bfloat16", _wide(), 5, 0.12)
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+def test_engine_on_cuda_randomly_drawn_stacks_fp32(tmp_path, seed):
+    from test_rumuvik import drawn_config
+
+    _need()
+    _engine_case(tmp_path, "float32", drawn_config(seed, friendly=seed % 2 == 0), seed, 2e-3, gen=False)
+
+
+@pytest.mark.parametrize("seed", [21, 22, 23])
+def test_engine_on_cuda_randomly_drawn_stacks_bf16(tmp_path, seed):
+    from test_rumuvik import drawn_config
+
+    _need()
+    _engine_case(tmp_path, "bfloat16", drawn_config(seed, friendly=True), seed, 0.2)
