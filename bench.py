@@ -50,9 +50,10 @@ def parse_args():
                     help="instead of the default workload: Rirotar beside Qwen3-Next at equal size (engine prefill / decode) and its kernels beside "
                          "the like ops, one JSON line per measurement (sglang_b200/benchmark/hybrid_compare.py)")
     ap.add_argument("--hybrid-sizes", default="2048,4096", help="model widths of --hybrid-compare")
-    ap.add_argument("--hybrid-family", default="rirotar", choices=("rirotar", "zaparax", "resatar"),
+    ap.add_argument("--hybrid-family", default="rirotar", choices=("rirotar", "zaparax", "resatar", "rumuvik"),
                     help="which per-layer hybrid family --hybrid-compare measures: rirotar beside Qwen3-Next, zaparax beside Nemotron-H "
-                         "(sglang_b200/benchmark/zaparax_compare.py), or resatar beside Jamba (sglang_b200/benchmark/resatar_compare.py)")
+                         "(sglang_b200/benchmark/zaparax_compare.py), resatar beside Jamba (sglang_b200/benchmark/resatar_compare.py), or rumuvik beside "
+                         "Resatar (sglang_b200/benchmark/rumuvik_compare.py)")
     return ap.parse_args()
 
 
@@ -203,6 +204,8 @@ def main() -> None:
             from sglang_b200.benchmark.zaparax_compare import main as hybrid_main
         elif args.hybrid_family == "resatar":
             from sglang_b200.benchmark.resatar_compare import main as hybrid_main
+        elif args.hybrid_family == "rumuvik":
+            from sglang_b200.benchmark.rumuvik_compare import main as hybrid_main
         else:
             from sglang_b200.benchmark.hybrid_compare import main as hybrid_main
 
