@@ -493,9 +493,9 @@ void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt
 //   decay_t = exp(f + m_(t-1) - m_t), step_t = exp(i - m_t), floor_t = exp(-m_t).
 // With those the memory S_t = decay_t S_(t-1) + step_t k v^T and its normaliser n_t (the same recurrence on a value that is always 1) run on
 // mamba2_scan(gates): x = [v | 1] per head, B = k, C = q / sqrt(D).
-// mlstm_prepare, one launch with two kinds of CTA: the first T write a token's [x | B | C] row in fp32; the others hold four warps, a warp per
-// (request, head), which walks m through the request's tokens 32 at a time (gate activations lane-parallel, the max-chain by shuffles, the three
-// exponentials lane-parallel again) and leaves m in mstate [slots, H].  Everything fp32.
+// mlstm_prepare, one launch with two kinds of CTA: the first hold four warps, a warp per (request, head), which walks m through the
+// request's tokens 32 at a time (gate activations lane-parallel, the max-chain by shuffles, the three exponentials lane-parallel again) and
+// leaves m in mstate [slots, H]; the T CTAs behind them write a token's [x | B | C] row in fp32 each.  Everything fp32.
 // mlstm_readout: o = y[:Dv] / (max(|y[Dv]|, floor) + 1e-6) per head, divided by its root mean square, times weight, times sigmoid(gate); a warp
 // per (token, head).
 namespace {
@@ -512,14 +512,17 @@ __global__ void __launch_bounds__(128) mlstm_prepare_kernel(const T* __restrict_
                                                             float* __restrict__ mstate, const int* __restrict__ req_slots, const int* __restrict__ seq_lens,
                                                             const int* __restrict__ cu_q, int Tn, int B, float* __restrict__ u, float* __restrict__ gates) {
   const int tid = threadIdx.x;
-  if ((int)blockIdx.x < Tn) {
-    const int t = blockIdx.x;
+  const int gate_ctas = (B * H + 3) / 4;             // they come first: their serial walk overlaps the row conversion of the CTAs behind them
+  if ((int)blockIdx.x >= gate_ctas) {
+    const int t = blockIdx.x - gate_ctas;
     const T* row = proj + (size_t)t * ld;
     const int nk = H * D, P = Dv + 1, nx = H * P;
     float* dst = u + (size_t)t * (nx + 2 * nk);
-    for (int idx = tid; idx < nx; idx += 128) {
-      const int h = idx / P, c = idx - h * P;
-      dst[idx] = c < Dv ? ml_ld<T>(row + 2 * nk + h * Dv + c) : 1.f;
+    for (int h = 0; h < H; ++h) {
+      const T* src = row + 2 * nk + h * Dv;
+      float* d = dst + h * P;
+      for (int c = tid; c < Dv; c += 128) d[c] = ml_ld<T>(src + c);
+      if (tid == 0) d[Dv] = 1.f;
     }
     const float qs = 1.0f / sqrtf((float)D);
     for (int idx = tid; idx < nk; idx += 128) {
@@ -528,7 +531,7 @@ __global__ void __launch_bounds__(128) mlstm_prepare_kernel(const T* __restrict_
     }
     return;
   }
-  const int w = ((int)blockIdx.x - Tn) * 4 + (tid >> 5), lane = tid & 31;
+  const int w = (int)blockIdx.x * 4 + (tid >> 5), lane = tid & 31;
   if (w >= B * H) return;
   const int b = w / H, h = w - b * H;
   const int q0 = cu_q ? cu_q[b] : b;

@@ -47,6 +47,37 @@ class LatentCacheSpec:
         self.layer_id, self.scale, self.window, self.logit_cap, self.rope, self.sinks = layer_id, scale, window, 0.0, None, None
 
 
+def expand_plan(fb: ForwardBatch, window: int, page: int):
+    """which cached rows this forward's prompt portions can see, laid out as a scratch paged buffer of ``page``-token pages (built once per
+    forward and window on the host from the lengths the scheduler already holds; shared by all layers with that window)"""
+    plans = fb.__dict__.setdefault("_latent_expand", {})
+    W = window
+    if (W, page) in plans:
+        return plans[(W, page)]
+    ps, P = fb.page_size, page
+    sl, ql, slots = np.asarray(fb.seq_lens_cpu, dtype=np.int64), np.asarray(fb.q_lens_cpu, dtype=np.int64), fb.req_slots
+    lo = np.maximum(0, sl - ql - W + 1) if W > 0 else np.zeros_like(sl)
+    n = sl - lo
+    pages = (n + P - 1) // P
+    first = np.concatenate([[0], np.cumsum(pages)[:-1]]) + 1                      # (page 0 stays unused, like in the real pool)
+    B = len(sl)
+    pt = np.zeros((B, int(pages.max())), dtype=np.int32)
+    req = np.repeat(np.arange(B), n)
+    rel = np.concatenate([np.arange(k) for k in n])
+    for b in range(B):
+        pt[b, : pages[b]] = first[b] + np.arange(pages[b])
+    dev = fb.seq_lens.device
+    to = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True).to(dt)
+    pos = to(lo[req] + rel, torch.int64)
+    reqd = to(req, torch.int64)
+    src = fb.page_table[slots.long()[reqd], pos // ps].long() * ps + pos % ps           # rows of the latent cache
+    dst = to((first[req] * P + rel), torch.int64)                                       # rows of the scratch buffer
+    plan = {"src": src, "dst": dst, "rows": int((first[-1] + pages[-1]) * P), "pt": to(pt, torch.int32), "n": to(n, torch.int32),
+            "slots": torch.arange(B, dtype=torch.int32, device=dev), "max_n": int(n.max()), "total": int(n.sum())}
+    plans[(W, page)] = plan
+    return plan
+
+
 class WindowedLatentAttention(nn.Module):
     def __init__(self, width: int, heads: int, dim: int, vdim: int, kv_rank: int, scale: Optional[float], window: int, eps: float, layer_id: int,
                  dtype, cache_width: Optional[int] = None, sinks: bool = True):
@@ -92,34 +123,7 @@ class WindowedLatentAttention(nn.Module):
     expand_prefill = True            # class-wide switch of the expanded prompt route (tests compare it with the absorbed kernel)
 
     def _expand_plan(self, fb: ForwardBatch):
-        """which cached rows this forward's prompt portions can see, laid out as a scratch paged buffer (built once per forward and window
-        on the host from the lengths the scheduler already holds; shared by all layers with that window)"""
-        plans = fb.__dict__.setdefault("_latent_expand", {})
-        W = self.attn.window
-        if W in plans:
-            return plans[W]
-        ps, P = fb.page_size, self.EXPAND_PAGE
-        sl, ql, slots = np.asarray(fb.seq_lens_cpu, dtype=np.int64), np.asarray(fb.q_lens_cpu, dtype=np.int64), fb.req_slots
-        lo = np.maximum(0, sl - ql - W + 1) if W > 0 else np.zeros_like(sl)
-        n = sl - lo
-        pages = (n + P - 1) // P
-        first = np.concatenate([[0], np.cumsum(pages)[:-1]]) + 1                      # (page 0 stays unused, like in the real pool)
-        B = len(sl)
-        pt = np.zeros((B, int(pages.max())), dtype=np.int32)
-        req = np.repeat(np.arange(B), n)
-        rel = np.concatenate([np.arange(k) for k in n])
-        for b in range(B):
-            pt[b, : pages[b]] = first[b] + np.arange(pages[b])
-        dev = fb.seq_lens.device
-        to = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True).to(dt)
-        pos = to(lo[req] + rel, torch.int64)
-        reqd = to(req, torch.int64)
-        src = fb.page_table[slots.long()[reqd], pos // ps].long() * ps + pos % ps           # rows of the latent cache
-        dst = to((first[req] * P + rel), torch.int64)                                       # rows of the scratch buffer
-        plan = {"src": src, "dst": dst, "rows": int((first[-1] + pages[-1]) * P), "pt": to(pt, torch.int32), "n": to(n, torch.int32),
-                "slots": torch.arange(B, dtype=torch.int32, device=dev), "max_n": int(n.max())}
-        plans[W] = plan
-        return plan
+        return expand_plan(fb, self.attn.window, self.EXPAND_PAGE)
 
     def _forward_expanded(self, q: torch.Tensor, cache: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         T, H, D = q.shape[0], self.H, self.D
@@ -229,12 +233,46 @@ class RotaryLatentAttention(nn.Module):
             self._uv32 = self.uv.detach().float().view(self.H, self.Dv, self.R).transpose(1, 2).contiguous()  # [H, R, Dv]
         return self._uk32, self._uv32
 
+    EXPAND_PAGE = 64
+    expand_prefill = True            # class-wide switch of the expanded prompt route (tests compare it with the absorbed kernel)
+
+    def _wants_expanded(self, fb: ForwardBatch, T: int) -> bool:
+        """prompt portions that make up a fair share of what they see: per (query, key, head) the expanded form costs ``dim + rot_dim + vdim``
+        multiply-adds, the absorbed one ``2 kv_rank + rot_dim``, but it up-projects every visible row first"""
+        if not (self.expand_prefill and fb.cu_q is not None and fb.max_q_len > 1 and T >= 64 and fb.q_lens_cpu is not None and fb.seq_lens_cpu is not None
+                and self.D + self.Dr <= 256 and self.Dv <= 256 and self.D + self.Dr + self.Dv < 2 * self.R + self.Dr):
+            return False
+        return int(np.sum(np.asarray(fb.seq_lens_cpu, dtype=np.int64))) <= 16 * T
+
+    def _forward_expanded(self, q: torch.Tensor, cache: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        """the visible cache rows are gathered once, up-projected to per-head keys ``[W_uk,h c | rotary key]`` and values ``W_uv,h c`` in a
+        scratch paged buffer, and the framework's general attention kernel runs over them (the queries' rotary part turned in place)"""
+        T, H, D, Dr, R, Dv = q.shape[0], self.H, self.D, self.Dr, self.R, self.Dv
+        pl = expand_plan(fb, self.window, self.EXPAND_PAGE)
+        rows = cache[pl["src"], 0, : R + Dr]                                                # [N, R + Dr] visible rows
+        c = rows[:, :R].contiguous()
+        nk, nv = H * (D + Dr), H * Dv
+        buf = torch.zeros(pl["rows"], nk + nv, dtype=q.dtype, device=q.device)              # one row = [keys of all heads | values of all heads]
+        k = torch.empty(rows.shape[0], H, D + Dr, dtype=q.dtype, device=q.device)
+        k[:, :, :D] = ops.linear(c, self.uk).view(-1, H, D)
+        k[:, :, D:] = rows[:, None, R:]
+        buf[pl["dst"], :nk] = k.view(-1, nk)
+        buf[pl["dst"], nk:] = ops.linear(c, self.uv)
+        if Dr:
+            qr = ops.latent_query(q, torch.empty(H, T, 0, dtype=torch.float32, device=q.device), D, Dr, fb.positions, self.inv_freq, self.rot_mult)
+            q = torch.cat([q[:, :, :D], qr.to(q.dtype)], -1)
+        o = ops.window_attention(q.contiguous(), buf[:, None, :nk], buf[:, None, nk:], H, Dv, pl["pt"], pl["slots"], pl["n"], fb.cu_q, fb.q_lens, fb.max_q_len,
+                                 self.EXPAND_PAGE, self.scale, 0.0, self.window, None, None, D + Dr, 0)
+        return o.reshape(T, H * Dv)
+
     def forward(self, h: torch.Tensor, fb: ForwardBatch, cache: torch.Tensor) -> torch.Tensor:
         T, H, D, Dr, R = h.shape[0], self.H, self.D, self.Dr, self.R
         down = ops.linear(h, self.down_weight)
         cq = ops.latent_prepare(down, self.Rq, self.q_norm, R, Dr, self.kv_norm, self.eps, fb.positions, self.inv_freq, self.rot_mult, cache,
                                 fb.out_cache_loc)
         q = ops.linear(cq, self.uq).view(T, H, D + Dr)
+        if self._wants_expanded(fb, T):
+            return ops.linear(self._forward_expanded(q, cache, fb), self.o_weight)
         uk, uv = self._absorbed()
         q_abs = torch.bmm(q[:, :, :D].float().transpose(0, 1), uk)                                            # [H, T, R] fp32
         q_lat = ops.latent_query(q, q_abs, D, Dr, fb.positions, self.inv_freq, self.rot_mult)                 # [T, H, R + Dr] fp32

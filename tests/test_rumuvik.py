@@ -369,6 +369,34 @@ def test_one_and_two_layer_models(tmp_path, cfg):
     h.close()
 
 
+def test_expanded_prompt_route_of_latent_attention(tmp_path, monkeypatch):
+    """large prompt portions up-project the rows they see and run the general attention kernel; small ones and decode tokens stay absorbed:
+    both against the oracle, alone and in one batch, and the route is really taken"""
+    from sglang_b200.layers.latent_attention import RotaryLatentAttention
+
+    calls = []
+    real = RotaryLatentAttention._forward_expanded
+    monkeypatch.setattr(RotaryLatentAttention, "_forward_expanded", lambda self, q, cache, fb: (calls.append(q.shape[0]), real(self, q, cache, fb))[1])
+    h = Harness(tmp_path, _cfg([L(_lat(), _dense()), L(_lat(heads=2, dim=4, rot_dim=0, vdim=4, kv_rank=5, q_rank=3, scaling=None), None)]), max_tokens=60 * PAGE)
+    a, b = _tokens(150, 50, 1), _tokens(90, 50, 2)
+    ra, rb = h.oracle(a), h.oracle(b)
+    _close(h.step([("a", a, range(len(a)))], ["a"]), ra)
+    assert calls == [150, 150]
+    _close(h.run_cut("a2", a, [70, 3, 66]), ra)                                    # expanded, absorbed, expanded over cached rows, then token by token
+    assert calls[2:] == [70, 70, 66, 66]
+    out = h.step([("a", a[:80], range(80)), ("b", b[:5], range(5))], [])           # a large and a small portion in one batch
+    _close(out[:80], ra[:80]); _close(out[80:], rb[:5])
+    out = h.step([("a", a[80:81], range(1)), ("b", b[5:], range(85))], ["b"])      # a decode token beside a large portion
+    _close(out[:1], ra[80:81]); _close(out[1:], rb[5:])
+    n = len(calls)
+    _close(h.step([("a", a[81:], range(69))], ["a"]), ra[81:])
+    assert len(calls) == n + 2
+    monkeypatch.setattr(RotaryLatentAttention, "expand_prefill", False)
+    _close(h.step([("c", a, range(len(a)))], ["c"]), ra)
+    assert len(calls) == n + 2
+    h.close()
+
+
 # ------------------------------------------------------------------ the mixed model: cuts, batches, reuse
 @pytest.fixture(scope="module")
 def mixed(tmp_path_factory):
