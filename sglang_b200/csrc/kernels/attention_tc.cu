@@ -21,6 +21,13 @@
 
 namespace sglb {
 
+// tanh(z) = 1 - 2 / (exp(2 z) + 1) on the two fast special-function instructions (ex2, rcp): no branch between a polynomial and an exponential
+// form as in tanhf; absolute error about 2e-7 (the cap multiplies it), exact limits (+-1) where the exponential over- or underflows
+__device__ __forceinline__ float tanh_by_exp(float z) {
+  const float t = ex2_approx(z * 2.8853900817779268f);
+  return 1.f - __fdividef(2.f, t + 1.f);
+}
+
 constexpr int ATT_D = 128;          // head dim
 // kv tile KT is a template parameter: 128 for prefill (compute-bound, 1 CTA/SM), 64 for decode (latency-bound: 256
 // TMEM columns + 96 KB smem so two CTAs share an SM and overlap their load -> MMA -> softmax chains)
@@ -266,7 +273,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float x = __uint_as_float(sr[c][i]) * scale_nat;
-              const float y = cap > 0.f ? cap * tanhf(x * inv_cap) : x;
+              const float y = cap > 0.f ? cap * tanh_by_exp(x * inv_cap) : x;
               sr[c][i] = __float_as_uint(fmaf(slope, (float)(c * 32 + i), y + off) * inv_scale_nat);
             }
         }
@@ -683,7 +690,7 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const float x = __uint_as_float(sr[c][i]) * scale_nat;
-                const float y = cap > 0.f ? cap * tanhf(x * inv_cap) : x;
+                const float y = cap > 0.f ? cap * tanh_by_exp(x * inv_cap) : x;
                 sr[c][i] = __float_as_uint(fmaf(slope, (float)(c * 32 + i), y + off) * inv_scale_nat);
               }
           }

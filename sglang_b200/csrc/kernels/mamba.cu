@@ -574,18 +574,18 @@ __global__ void __launch_bounds__(128) mlstm_readout_kernel(const float* __restr
   if (row >= rows) return;
   const int t = row / H, h = row - t * H;
   const float* yy = y + (size_t)row * (Dv + 1);
-  const float den = fmaxf(fabsf(yy[Dv]), gates[(size_t)row * 3 + 2]) + 1e-6f;
+  const float inv = 1.0f / (fmaxf(fabsf(yy[Dv]), gates[(size_t)row * 3 + 2]) + 1e-6f);
   float ss = 0.f;
   for (int c = lane; c < Dv; c += 32) {
-    const float o = yy[c] / den;
+    const float o = yy[c] * inv;
     ss += o * o;
   }
-  const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+  const float rs = inv / sqrtf(warp_sum(ss) / (float)Dv + eps);
   const TO* wr = w + (size_t)h * Dv;
   const TO* gr = gate ? gate + (size_t)t * ldg + (size_t)h * Dv : nullptr;
   TO* dst = out + (size_t)row * Dv;
   for (int c = lane; c < Dv; c += 32) {
-    float v = yy[c] / den * rs * ml_ld<TO>(wr + c);
+    float v = yy[c] * rs * ml_ld<TO>(wr + c);
     if (gr) v *= 1.f / (1.f + expf(-ml_ld<TO>(gr + c)));
     ml_st<TO>(dst + c, v);
   }

@@ -342,26 +342,33 @@ __global__ void __launch_bounds__(128) sigmoid_gate_kernel(const T* __restrict__
 }
 
 // out[t, h * Dv + c] = the head o[t, h, :Dv] (rows of hs elements) times sigmoid(lse[t, h] - sink[h]) (lse null: times 1), turned over its whole
-// width by -+ position * inv_freq[m]: pair m = columns (m, m + Dv/2) or, inter, (2m, 2m + 1).  Angle, sine and cosine fp32.
+// width by -+ position * inv_freq[m]: pair m = columns (m, m + Dv/2) or, inter, (2m, 2m + 1).  Angle, sine and cosine fp32.  One CTA per token:
+// a thread owns a pair index and walks the heads, so that the sine and cosine of an angle are computed once for all heads.
 template <typename T>
 __global__ void __launch_bounds__(128) rotate_heads_kernel(const T* __restrict__ o, int hs, const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                                           int rows, int H, int Dv, int inter, float sign, const float* __restrict__ lse,
+                                                           int H, int Dv, int inter, float sign, const float* __restrict__ lse,
                                                            const float* __restrict__ sinks, T* __restrict__ out) {
+  const int t = blockIdx.x;
   const int hv = Dv >> 1;
-  const size_t idx = (size_t)blockIdx.x * 128 + threadIdx.x;          // one thread per (token, head, pair)
-  if (idx >= (size_t)rows * hv) return;
-  const int row = (int)(idx / hv), m = (int)(idx - (size_t)row * hv);
-  const int t = row / H;
-  const float gte = lse ? 1.f / (1.f + expf(sinks[row - t * H] - lse[row])) : 1.f;
-  const T* src = o + (size_t)row * hs;
-  T* dst = out + (size_t)row * Dv;
-  const int ia = inter ? 2 * m : m, ib = inter ? 2 * m + 1 : m + hv;
-  const float a = wa_ld<T>(src + ia) * gte, b = wa_ld<T>(src + ib) * gte;
-  float sn, cs;
-  sincosf((float)positions[t] * inv_freq[m], &sn, &cs);
-  sn *= sign;
-  wa_st<T>(dst + ia, a * cs - b * sn);
-  wa_st<T>(dst + ib, b * cs + a * sn);
+  const int pw = hv >= 128 ? 128 : hv;               // threads across the pairs of a head; the others of the CTA take further heads
+  const int hstep = 128 / pw, h0 = threadIdx.x / pw;
+  if (h0 >= hstep) return;
+  const float pos = (float)positions[t];
+  for (int m = threadIdx.x - h0 * pw; m < hv; m += pw) {
+    float sn, cs;
+    sincosf(pos * inv_freq[m], &sn, &cs);
+    sn *= sign;
+    const int ia = inter ? 2 * m : m, ib = inter ? 2 * m + 1 : m + hv;
+    for (int h = h0; h < H; h += hstep) {
+      const size_t row = (size_t)t * H + h;
+      const float gte = lse ? 1.f / (1.f + expf(sinks[h] - lse[row])) : 1.f;
+      const T* src = o + row * hs;
+      T* dst = out + row * Dv;
+      const float a = wa_ld<T>(src + ia) * gte, b = wa_ld<T>(src + ib) * gte;
+      wa_st<T>(dst + ia, a * cs - b * sn);
+      wa_st<T>(dst + ib, b * cs + a * sn);
+    }
+  }
 }
 
 struct PrepParams {
@@ -595,12 +602,12 @@ void rotate_heads(const void* o, int head_stride, bool bf16, const int* position
                   const float* lse, const float* sinks, void* out, cudaStream_t stream) {
   if (T <= 0 || H <= 0) return;
   const float sign = inverse ? -1.f : 1.f;
-  const unsigned grid = (unsigned)(((size_t)T * H * (Dv / 2) + 127) / 128);
+  const unsigned grid = (unsigned)T;
   if (bf16)
-    rotate_heads_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)o, head_stride, positions, inv_freq, T * H, H, Dv, interleaved ? 1 : 0, sign,
+    rotate_heads_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)o, head_stride, positions, inv_freq, H, Dv, interleaved ? 1 : 0, sign,
                                                                   lse, sinks, (__nv_bfloat16*)out);
   else
-    rotate_heads_kernel<float><<<grid, 128, 0, stream>>>((const float*)o, head_stride, positions, inv_freq, T * H, H, Dv, interleaved ? 1 : 0, sign, lse, sinks,
+    rotate_heads_kernel<float><<<grid, 128, 0, stream>>>((const float*)o, head_stride, positions, inv_freq, H, Dv, interleaved ? 1 : 0, sign, lse, sinks,
                                                           (float*)out);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }

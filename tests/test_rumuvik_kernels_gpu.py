@@ -375,3 +375,13 @@ def test_engine_on_cuda_randomly_drawn_stacks_bf16(tmp_path, seed):
 
     _need()
     _engine_case(tmp_path, "bfloat16", drawn_config(seed, friendly=True), seed, 0.15, spikes=True)
+
+
+@pytest.mark.parametrize("seed", [31, 32, 33])
+def test_engine_on_cuda_randomly_drawn_stacks_of_odd_sizes_bf16(tmp_path, seed):
+    """widths, head sizes, ranks and vocabularies that are no multiples of the vector widths: every kernel takes its scalar path, the GEMMs
+    their general one"""
+    from test_rumuvik import drawn_config
+
+    _need()
+    _engine_case(tmp_path, "bfloat16", drawn_config(seed), seed, 0.25, spikes=True)
