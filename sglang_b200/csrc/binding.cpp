@@ -712,6 +712,17 @@ void mlstm_readout(const at::Tensor& y, const at::Tensor& gates, int64_t H, int6
   count();
 }
 
+void causal_softmax(const at::Tensor& scores, int64_t tq, int64_t first, double scale, at::Tensor out) {
+  CHECK_CUDA(scores);
+  TORCH_CHECK(scores.scalar_type() == at::kFloat && scores.dim() == 2 && scores.is_contiguous() && bf16_or_f32(out) && out.is_contiguous() &&
+              out.numel() == scores.numel() && tq >= 1 && scores.size(0) % tq == 0 && first >= 0);
+  if (scores.numel() == 0) return;
+  c10::cuda::CUDAGuard g(scores.device());
+  sglb::causal_softmax(scores.data_ptr<float>(), out.data_ptr(), out.scalar_type() == at::kBFloat16, (int)scores.size(0), (int)tq, (int)scores.size(1), (int)first,
+                       (float)scale, cur_stream());
+  count();
+}
+
 // bench tool: per-role cycle accounting of the decode attention kernel into buf [ctas * 30] (int64); an empty tensor turns it off
 void attn_decode_prof(const at::Tensor& buf) {
   if (buf.numel() == 0) { sglb::attn_decode_set_prof(nullptr); return; }
@@ -1155,6 +1166,7 @@ TORCH_LIBRARY(sglb, m) {
   m.def("latent_prepare(Tensor x, int q_rank, Tensor? q_norm_w, int rank, int rot_dim, Tensor kv_norm_w, float eps, Tensor positions, Tensor? inv_freq, "
         "float mult, Tensor(a!) cache, Tensor loc, Tensor(b!)? cq) -> ()", &latent_prepare);
   m.def("latent_query(Tensor q, Tensor q_abs, int dim, int rot_dim, Tensor positions, Tensor? inv_freq, float mult, Tensor(a!) out) -> ()", &latent_query);
+  m.def("causal_softmax(Tensor scores, int tq, int first, float scale, Tensor(a!) out) -> ()", &causal_softmax);
   m.def("rotate_heads(Tensor o, Tensor positions, Tensor inv_freq, int Dv, bool interleaved, bool inverse, Tensor? lse, Tensor? sinks, Tensor(a!) out) -> ()",
         &rotate_heads);
   m.def("parallel_add_rmsnorm_f32(Tensor(a!) residual, Tensor? d1, Tensor? d2, Tensor? d3, Tensor w1, Tensor? w2, Tensor(b!) out1, Tensor(c!)? out2, float eps, "

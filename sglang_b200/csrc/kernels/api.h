@@ -124,6 +124,7 @@ void attention_prepare(const void* qkv, int ld, bool bf16, int T, int H, int G, 
                        void* q_out, int pad, const float* v_inv_freq, bool v_interleaved, cudaStream_t stream);
 void rotate_heads(const void* o, int head_stride, bool bf16, const int* positions, const float* inv_freq, int T, int H, int Dv, bool interleaved, bool inverse,
                   const float* lse, const float* sinks, void* out, cudaStream_t stream);
+void causal_softmax(const float* scores, void* out, bool out_bf16, int rows, int tq, int n, int first, float scale, cudaStream_t stream);
 void attention_sink_gate(const void* o, int ldo, const float* lse, const float* sinks, int rows, int H, int Dv, void* out, cudaStream_t stream);
 // mamba.cu (ragged Mamba-2 recurrence), residual_f32.cu (sandwich norms), elementwise.cu (bigram embedding), moe.cu (identity / shared experts)
 void mamba2_scan(const float* u, int ldu, const void* z, int ldz, const void* dt_raw, int lddt, bool bf16, const float* dt_bias, const float* A_log,

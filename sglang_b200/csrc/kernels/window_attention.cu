@@ -371,6 +371,37 @@ __global__ void __launch_bounds__(128) rotate_heads_kernel(const T* __restrict__
   }
 }
 
+// rows of raw scores -> soft-max weights under a causal limit, for attention that runs as two matrix products around this kernel:
+// s fp32 [R, n], row r = h * tq + i belongs to query i of its request portion and sees keys j <= first + i;
+// out[r, j] = exp(scale * s[r, j] - m) / sum over the visible keys (0 beyond them), m the row's largest visible scaled score.  One CTA per row.
+template <typename TO>
+__global__ void __launch_bounds__(256) causal_softmax_kernel(const float* __restrict__ s, TO* __restrict__ out, int tq, int n, int first, float scale) {
+  __shared__ float red[8];
+  const size_t row = blockIdx.x;
+  const int lim = min(n, first + (int)(row % tq) + 1);
+  const float* sr = s + row * n;
+  TO* orow = out + row * n;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < lim; j += 256) m = fmaxf(m, sr[j] * scale);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+  __syncthreads();
+  float l = 0.f;
+  for (int j = threadIdx.x; j < lim; j += 256) l += wa_exp<TO>(sr[j] * scale - m);
+  l = warp_sum(l);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = l;
+  __syncthreads();
+  l = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) l += red[i];
+  const float inv = 1.f / l;
+  for (int j = threadIdx.x; j < n; j += 256) wa_st<TO>(orow + j, j < lim ? wa_exp<TO>(sr[j] * scale - m) * inv : 0.f);
+}
+
 struct PrepParams {
   const void* qkv; int ld;                     // rows [q (H*D) | k (G*D) | v (G*Dv) | ...]
   int H, G, D, Dv;
@@ -609,6 +640,13 @@ void rotate_heads(const void* o, int head_stride, bool bf16, const int* position
   else
     rotate_heads_kernel<float><<<grid, 128, 0, stream>>>((const float*)o, head_stride, positions, inv_freq, H, Dv, interleaved ? 1 : 0, sign, lse, sinks,
                                                           (float*)out);
+  SGLB_CUDA_CHECK(cudaGetLastError());
+}
+
+void causal_softmax(const float* scores, void* out, bool out_bf16, int rows, int tq, int n, int first, float scale, cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return;
+  if (out_bf16) causal_softmax_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(scores, (__nv_bfloat16*)out, tq, n, first, scale);
+  else causal_softmax_kernel<float><<<rows, 256, 0, stream>>>(scores, (float*)out, tq, n, first, scale);
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -23,7 +23,9 @@ The window only masks: pages of tokens that left the window are still held until
 ``RotaryLatentAttention`` is the positional form: queries pass a normed latent of their own, every head has ``dim`` unrotated and
 ``rot_dim`` rotary query / key coordinates, and ONE rotary key part per token is shared by all heads.  The cache row is
 ``[c (kv_rank) | rotary key (rot_dim)]``; in the absorbed form the query is ``[W_uk,h^T q_h | rotary part]`` and the same kernel scores over
-the whole row while only its first ``kv_rank`` columns are values (``ops.latent_attention(v_rank=...)``).
+the whole row while only its first ``kv_rank`` columns are values (``ops.latent_attention(v_rank=...)``).  Large prompt portions take the
+expanded form over up-projected rows: on the general attention kernel (keys up to 256 wide, fp32 and bf16), or, for long bf16 portions, as
+Q K^T and P V on the tensor cores (vendor batched GEMMs, fp32 scores) around ``ops.causal_softmax``.
 """
 from __future__ import annotations
 
@@ -73,7 +75,8 @@ def expand_plan(fb: ForwardBatch, window: int, page: int):
     src = fb.page_table[slots.long()[reqd], pos // ps].long() * ps + pos % ps           # rows of the latent cache
     dst = to((first[req] * P + rel), torch.int64)                                       # rows of the scratch buffer
     plan = {"src": src, "dst": dst, "rows": int((first[-1] + pages[-1]) * P), "pt": to(pt, torch.int32), "n": to(n, torch.int32),
-            "slots": torch.arange(B, dtype=torch.int32, device=dev), "max_n": int(n.max()), "total": int(n.sum())}
+            "slots": torch.arange(B, dtype=torch.int32, device=dev), "max_n": int(n.max()), "total": int(n.sum()), "first_rows": first * P, "n_cpu": n,
+            "lo_cpu": lo}
     plans[(W, page)] = plan
     return plan
 
@@ -246,7 +249,8 @@ class RotaryLatentAttention(nn.Module):
 
     def _forward_expanded(self, q: torch.Tensor, cache: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         """the visible cache rows are gathered once, up-projected to per-head keys ``[W_uk,h c | rotary key]`` and values ``W_uv,h c`` in a
-        scratch paged buffer, and the framework's general attention kernel runs over them (the queries' rotary part turned in place)"""
+        scratch paged buffer (the queries' rotary part turned in place); over them runs the framework's general attention kernel or, for long
+        bf16 portions, two batched matrix products around a soft-max kernel (``_attend_by_gemms``)"""
         T, H, D, Dr, R, Dv = q.shape[0], self.H, self.D, self.Dr, self.R, self.Dv
         pl = expand_plan(fb, self.window, self.EXPAND_PAGE)
         rows = cache[pl["src"], 0, : R + Dr]                                                # [N, R + Dr] visible rows
@@ -261,9 +265,43 @@ class RotaryLatentAttention(nn.Module):
         if Dr:
             qr = ops.latent_query(q, torch.empty(H, T, 0, dtype=torch.float32, device=q.device), D, Dr, fb.positions, self.inv_freq, self.rot_mult)
             q = torch.cat([q[:, :, :D], qr.to(q.dtype)], -1)
-        o = ops.window_attention(q.contiguous(), buf[:, None, :nk], buf[:, None, nk:], H, Dv, pl["pt"], pl["slots"], pl["n"], fb.cu_q, fb.q_lens, fb.max_q_len,
+        q = q.contiguous()
+        if self.gemm_prefill and q.is_cuda and q.dtype == torch.bfloat16 and fb.max_q_len >= self.GEMM_MIN_Q and self.window <= 0 and ops.native_available():
+            return self._attend_by_gemms(q, buf, nk, pl, fb).reshape(T, H * Dv)
+        o = ops.window_attention(q, buf[:, None, :nk], buf[:, None, nk:], H, Dv, pl["pt"], pl["slots"], pl["n"], fb.cu_q, fb.q_lens, fb.max_q_len,
                                  self.EXPAND_PAGE, self.scale, 0.0, self.window, None, None, D + Dr, 0)
         return o.reshape(T, H * Dv)
+
+    GEMM_MIN_Q = 256
+    GEMM_SCORE_BYTES = 1 << 28
+    gemm_prefill = True              # class-wide switch of the two-product form of the expanded route (tests compare it with the attention kernel)
+
+    def _attend_by_gemms(self, q: torch.Tensor, buf: torch.Tensor, nk: int, pl: dict, fb: ForwardBatch) -> torch.Tensor:
+        """long bf16 prompt portions over the up-projected rows as two batched matrix products on the tensor cores around ``ops.causal_softmax``:
+        scores = Q K^T with fp32 results, soft-max weights in fp32 rounded to bf16 for the second product, out = P V.  The framework's tcgen05
+        attention kernels take 128-wide heads and these keys are ``dim + rot_dim`` wide; the score matrix goes through memory instead, in query
+        chunks of at most ``GEMM_SCORE_BYTES``.  Requests are walked on the host (their lengths are the scheduler's)."""
+        T, H, Dk = q.shape
+        Dv = self.Dv
+        out = torch.empty(T, H, Dv, dtype=q.dtype, device=q.device)
+        qs = 0
+        for b in range(len(pl["n_cpu"])):
+            tq, L, r0, n = int(fb.q_lens_cpu[b]), int(fb.seq_lens_cpu[b]), int(pl["first_rows"][b]), int(pl["n_cpu"][b])
+            if tq <= 0:
+                continue
+            rows = buf[r0:r0 + n]
+            kb = rows[:, :nk].unflatten(1, (H, Dk)).permute(1, 2, 0)                        # [H, Dk, n] (a view)
+            vb = rows[:, nk:].unflatten(1, (H, Dv)).permute(1, 0, 2)                        # [H, n, Dv]
+            qb = q[qs:qs + tq].transpose(0, 1)                                              # [H, tq, Dk]
+            step = max(16, min(tq, self.GEMM_SCORE_BYTES // (4 * H * max(1, L))))
+            for c0 in range(0, tq, step):
+                c1 = min(tq, c0 + step)
+                kmax = L - tq + c1                                                          # keys the chunk's last query sees
+                sc = torch.bmm(qb[:, c0:c1], kb[:, :, :kmax], out_dtype=torch.float32)      # [H, c, kmax] fp32
+                pw = ops.causal_softmax(sc.view(H * (c1 - c0), kmax), c1 - c0, L - tq + c0, self.scale, q.dtype)
+                out[qs + c0:qs + c1] = torch.bmm(pw.view(H, c1 - c0, kmax), vb[:, :kmax]).transpose(0, 1)
+            qs += tq
+        return out
 
     def forward(self, h: torch.Tensor, fb: ForwardBatch, cache: torch.Tensor) -> torch.Tensor:
         T, H, D, Dr, R = h.shape[0], self.H, self.D, self.Dr, self.R

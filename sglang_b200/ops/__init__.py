@@ -753,6 +753,17 @@ def rotate_heads(o: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
     return y
 
 
+def causal_softmax(scores: torch.Tensor, tq: int, first: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """soft-max weights of raw scores under a causal limit, for attention that runs as two matrix products around it: ``scores`` fp32 [R, n]
+    contiguous, row ``r = h * tq + i`` sees keys ``j <= first + i``; scale, maximum, exponential and sum in fp32, weights out in ``out_dtype``
+    (csrc/kernels/window_attention.cu)"""
+    if _use_native(scores) and scores.dtype == torch.float32 and scores.dim() == 2 and scores.is_contiguous() and out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(scores.shape, dtype=out_dtype, device=scores.device)
+        torch.ops.sglb.causal_softmax(scores, int(tq), int(first), float(scale), out)
+        return out
+    return torch_ref.causal_softmax(scores, tq, first, scale, out_dtype)
+
+
 def parallel_add_rmsnorm_f32(residual: torch.Tensor, deltas, w1: torch.Tensor, w2: Optional[torch.Tensor], eps: float, zero_centred: bool = False,
                              out_dtype: torch.dtype = torch.bfloat16, extra: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """fp32 residual stream of blocks whose branches read the same input: ``residual += sum(deltas) + extra`` (in place; ``deltas``: up to two

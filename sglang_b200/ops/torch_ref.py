@@ -755,6 +755,14 @@ def rotate_heads(o: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
     return rotate_pairs(x, positions, inv_freq, interleaved, inverse).reshape(T, H * Dv).to(o.dtype)
 
 
+def causal_softmax(scores: torch.Tensor, tq: int, first: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """scores fp32 [R, n], row r = h * tq + i: the soft-max of ``scale * scores[r]`` over the keys ``j <= first + i`` (zero beyond them), in ``out_dtype``"""
+    R, n = scores.shape
+    i = torch.arange(R, device=scores.device) % tq
+    hide = torch.arange(n, device=scores.device)[None, :] > (first + i)[:, None]
+    return torch.softmax((scores.float() * scale).masked_fill(hide, float("-inf")), -1).to(out_dtype)
+
+
 def parallel_add_rmsnorm_f32(residual: torch.Tensor, deltas, w1: torch.Tensor, w2: Optional[torch.Tensor], eps: float, zero_centred: bool,
                              out_dtype: torch.dtype):
     """residual (fp32, in place) += sum of ``deltas`` (fp32 sum of the deltas first); returns the RMS norm of the new residual under ``w1``

@@ -341,6 +341,19 @@ def test_gated_memory_in_portions_and_a_write_read_back_far_later():
     assert float(g2[2, 0, 1]) == 1.0 and float(g2[2, 0, 2]) < 1e-20 and float(g2[:, 0, :2].max()) <= 1.0 and abs(float(ms2) - (50.0 + 3 * math.log(0.5))) < 1e-4
 
 
+def test_causal_softmax_reference_op():
+    g = torch.Generator().manual_seed(9)
+    H, tq, n, first = 3, 5, 9, 2
+    s = torch.randn(H * tq, n, generator=g) * 3
+    p = torch_ref.causal_softmax(s, tq, first, 0.7, torch.float32)
+    for r in range(H * tq):
+        lim = min(n, first + r % tq + 1)
+        e = [math.exp(0.7 * float(s[r, j])) for j in range(lim)]
+        for j in range(n):
+            want = e[j] / sum(e) if j < lim else 0.0
+            assert abs(float(p[r, j]) - want) < 1e-6
+
+
 def test_config_reader(tmp_path):
     from sglang_b200.configs.model_config import load_model_config
 

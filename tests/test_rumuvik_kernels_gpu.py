@@ -385,3 +385,55 @@ def test_engine_on_cuda_randomly_drawn_stacks_of_odd_sizes_bf16(tmp_path, seed):
 
     _need()
     _engine_case(tmp_path, "bfloat16", drawn_config(seed), seed, 0.25, spikes=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,tq,n,first", [(3, 5, 9, 2), (2, 64, 300, 236), (4, 33, 33, 0), (1, 7, 1000, 10), (2, 3, 5000, 4996)])
+def test_causal_softmax(H, tq, n, first, dtype):
+    _need()
+    g = torch.Generator().manual_seed(n)
+    s = torch.randn(H * tq, n, generator=g) * 4
+    for scale in (0.3, 1.0):
+        ref = torch_ref.causal_softmax(s, tq, first, scale, dtype)
+        got = ops.causal_softmax(s.to(DEV), tq, first, scale, dtype)
+        torch.testing.assert_close(got.cpu().float(), ref.float(), **_tol(dtype, f32=(1e-5, 1e-6), bf=(1e-2, 1e-3)))
+        assert float(got[:, min(n, first + tq):].abs().max()) == 0.0 if first + tq < n else True
+
+
+def test_latent_prompts_as_two_matrix_products(tmp_path, monkeypatch):
+    """long bf16 prompt portions of latent attention run Q K^T and P V as batched GEMMs around the soft-max kernel: against the oracle, beside the
+    attention-kernel form of the same route, alone, over cached rows, and beside short portions and decode tokens of other requests"""
+    from sglang_b200.layers.latent_attention import RotaryLatentAttention
+    from test_rumuvik import Harness, L, _cfg, _dense, _lat, _tokens
+
+    _need()
+    calls = []
+    real = RotaryLatentAttention._attend_by_gemms
+    monkeypatch.setattr(RotaryLatentAttention, "_attend_by_gemms", lambda self, *a: (calls.append(1), real(self, *a))[1])
+    monkeypatch.setattr(RotaryLatentAttention, "GEMM_SCORE_BYTES", 1 << 18)              # several query chunks per request
+    cfg = _cfg([L(_lat(heads=4, dim=32, rot_dim=16, vdim=48, kv_rank=64, q_rank=48, scale=0.15), _dense(64)),
+                L(_lat(heads=2, dim=64, rot_dim=0, vdim=32, kv_rank=96, q_rank=32, scaling=None, scale=0.12), None)], width=128, vocab=256, scale=4.0)
+    h = Harness(tmp_path, cfg, seed=7, slots=4, max_tokens=2048, device="cuda", dtype="bfloat16", page=16)
+    a, b, c = _tokens(700, 256, 1), _tokens(300, 256, 2), _tokens(40, 256, 3)
+    ra, rb, rc = h.oracle(a), h.oracle(b), h.oracle(c)
+
+    def err(x, y):
+        d, r = x - y, y - y.mean(-1, keepdims=True)
+        d = d - d.mean(-1, keepdims=True)
+        return np.sqrt((d ** 2).mean(-1)) / np.sqrt((r ** 2).mean(-1) + 1e-12)
+
+    e1 = err(h.step([("a", a, range(len(a)))], ["a"]), ra)                                # one long prompt
+    assert len(calls) == 2
+    out = h.step([("a", a[:300], range(300)), ("b", b[:5], range(5)), ("c", c, range(40))], ["c"])
+    e2 = np.concatenate([err(out[:300], ra[:300]), err(out[300:305], rb[:5]), err(out[305:], rc)])
+    out = h.step([("a", a[300:], range(400)), ("b", b[5:6], range(1))], ["a"])           # 400 more over 300 cached rows, beside a decode token
+    e3 = np.concatenate([err(out[:400], ra[300:]), err(out[400:], rb[5:6])])
+    out = h.step([("b", b[6:], range(294))], ["b"])
+    e4 = err(out, rb[6:])
+    assert len(calls) == 8
+    monkeypatch.setattr(RotaryLatentAttention, "gemm_prefill", False)
+    e0 = err(h.step([("a", a, range(len(a)))], ["a"]), ra)                                # the same route on the attention kernel
+    assert len(calls) == 8
+    h.close()
+    for e in (e1, e2, e3, e4):
+        assert float(e.max()) < 0.1 and float(e.mean()) < 1.5 * float(e0.mean()) + 0.005, (float(e.max()), float(e.mean()), float(e0.mean()))
