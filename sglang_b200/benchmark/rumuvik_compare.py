@@ -12,7 +12,7 @@ Two parts, random weights, one GPU:
    feeds that scan; ``mlstm_readout`` vs the gated norm; causal attention on the tcgen05 kernels with a score cap + the sink / back-rotation
    pass vs the same kernels + the gate pass; the general kernel (fp32 serving, group sizes that do not divide 128) with cap and sink + the
    back-rotation pass vs the tcgen05 kernels; ``attention_prepare`` with rotated values vs with the value blend; the absorbed latent kernel
-   with 64 score-only columns vs the same kernel over the latent alone; ``latent_prepare`` vs the bf16 RMS norm; ``latent_query`` vs the
+   with 64 score-only columns vs the same kernel over the latent alone; ``causal_softmax`` vs ``torch.softmax`` + cast; ``latent_prepare`` vs the bf16 RMS norm; ``latent_query`` vs the
    transposing copy it replaces; the two-norm residual kernel vs two calls of the one-norm kernel; the gated activation vs ``silu_and_mul``.
    Roofline: algorithmic bytes over the measured copy bandwidth; for prompt attention also FLOPs over the measured bf16 GEMM rate.
 
@@ -189,6 +189,13 @@ def _kernel_numbers(timer: _Timer, hbm_gbs: float, tflops: float) -> List[dict]:
         nb = B * S * (R + Dr) * 2 + qa.numel() * 4 + B * Q * Hl * R * 4
         rec("latent_attention (absorbed, 64 score-only rotary columns)", ph, f"B{B} S{S} q{Q} H{Hl} R{R}+{Dr}", ms, nb,
             "latent_attention (the latent alone, same kernel)", like, like_bytes=B * S * R * 2 + qb.numel() * 8)
+    # the soft-max between the two matrix products of long latent prompt portions
+    tq = 2048
+    sc = torch.randn(Hl * tq, tq, device=dev, generator=g)
+    ms = timer(lambda: ops.causal_softmax(sc, tq, 0, 0.07, bf))
+    like = timer(lambda: torch.softmax(sc, -1).to(bf))
+    rec("causal_softmax (fp32 scores in, bf16 weights out, causal limit)", "prefill", f"H{Hl} q{tq} keys{tq}", ms, sc.numel() * 4,
+        "torch.softmax + cast (no mask; the same task's bytes)", like)
     T, Rq = 8192, 1536
     x = torch.randn(T, Rq + R + Dr, device=dev, generator=g).to(bf)
     wq, wk = torch.ones(Rq, device=dev, dtype=bf), torch.ones(R, device=dev, dtype=bf)

@@ -374,15 +374,25 @@ __global__ void __launch_bounds__(128) rotate_heads_kernel(const T* __restrict__
 // rows of raw scores -> soft-max weights under a causal limit, for attention that runs as two matrix products around this kernel:
 // s fp32 [R, n], row r = h * tq + i belongs to query i of its request portion and sees keys j <= first + i;
 // out[r, j] = exp(scale * s[r, j] - m) / sum over the visible keys (0 beyond them), m the row's largest visible scaled score.  One CTA per row.
-template <typename TO>
+template <typename TO, int KEEP>
 __global__ void __launch_bounds__(256) causal_softmax_kernel(const float* __restrict__ s, TO* __restrict__ out, int tq, int n, int first, float scale) {
   __shared__ float red[8];
   const size_t row = blockIdx.x;
   const int lim = min(n, first + (int)(row % tq) + 1);
   const float* sr = s + row * n;
   TO* orow = out + row * n;
+  float v[KEEP > 0 ? KEEP : 1];                  // KEEP > 0: the row's visible scores stay in registers (n <= 256 * KEEP), read and exponentiated once
   float m = -INFINITY;
-  for (int j = threadIdx.x; j < lim; j += 256) m = fmaxf(m, sr[j] * scale);
+  if (KEEP > 0) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int j = threadIdx.x + k * 256;
+      v[k] = j < lim ? sr[j] * scale : -INFINITY;
+      m = fmaxf(m, v[k]);
+    }
+  } else {
+    for (int j = threadIdx.x; j < lim; j += 256) m = fmaxf(m, sr[j] * scale);
+  }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
@@ -391,7 +401,15 @@ __global__ void __launch_bounds__(256) causal_softmax_kernel(const float* __rest
   for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
   __syncthreads();
   float l = 0.f;
-  for (int j = threadIdx.x; j < lim; j += 256) l += wa_exp<TO>(sr[j] * scale - m);
+  if (KEEP > 0) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      v[k] = wa_exp<TO>(v[k] - m);               // exp(-inf) = 0 beyond the limit
+      l += v[k];
+    }
+  } else {
+    for (int j = threadIdx.x; j < lim; j += 256) l += wa_exp<TO>(sr[j] * scale - m);
+  }
   l = warp_sum(l);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = l;
   __syncthreads();
@@ -399,7 +417,15 @@ __global__ void __launch_bounds__(256) causal_softmax_kernel(const float* __rest
 #pragma unroll
   for (int i = 0; i < 8; ++i) l += red[i];
   const float inv = 1.f / l;
-  for (int j = threadIdx.x; j < n; j += 256) wa_st<TO>(orow + j, j < lim ? wa_exp<TO>(sr[j] * scale - m) * inv : 0.f);
+  if (KEEP > 0) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int j = threadIdx.x + k * 256;
+      if (j < n) wa_st<TO>(orow + j, v[k] * inv);
+    }
+  } else {
+    for (int j = threadIdx.x; j < n; j += 256) wa_st<TO>(orow + j, j < lim ? wa_exp<TO>(sr[j] * scale - m) * inv : 0.f);
+  }
 }
 
 struct PrepParams {
@@ -645,8 +671,13 @@ void rotate_heads(const void* o, int head_stride, bool bf16, const int* position
 
 void causal_softmax(const float* scores, void* out, bool out_bf16, int rows, int tq, int n, int first, float scale, cudaStream_t stream) {
   if (rows <= 0 || n <= 0) return;
-  if (out_bf16) causal_softmax_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(scores, (__nv_bfloat16*)out, tq, n, first, scale);
-  else causal_softmax_kernel<float><<<rows, 256, 0, stream>>>(scores, (float*)out, tq, n, first, scale);
+#define SGLB_CSM(TO, KEEP) causal_softmax_kernel<TO, KEEP><<<rows, 256, 0, stream>>>(scores, (TO*)out, tq, n, first, scale)
+  if (out_bf16) {
+    if (n <= 1024) SGLB_CSM(__nv_bfloat16, 4); else if (n <= 2048) SGLB_CSM(__nv_bfloat16, 8); else if (n <= 4096) SGLB_CSM(__nv_bfloat16, 16); else SGLB_CSM(__nv_bfloat16, 0);
+  } else {
+    if (n <= 1024) SGLB_CSM(float, 4); else if (n <= 2048) SGLB_CSM(float, 8); else if (n <= 4096) SGLB_CSM(float, 16); else SGLB_CSM(float, 0);
+  }
+#undef SGLB_CSM
   SGLB_CUDA_CHECK(cudaGetLastError());
 }
 
