@@ -163,6 +163,8 @@ class GatedAttention(nn.Module):
                                   v_first if self.value_mix else None, self.vmix, pad, self.v_inv_freq, self.v_interleaved)
         gate = proj[:, self.rows - self.n_g:self.rows] if self.n_g else None
         turn = self.v_inv_freq is not None
+        # where the back-rotation may write the caller's buffer directly: nothing follows it
+        direct = out if turn and gate is None and self.out_scale == 1.0 and out is not None and out.is_contiguous() else None
         if self.tc_route and pad == 128 and kc.shape[-1] >= G * 128:
             k4, v4 = kc[:, 0, :G * 128].unflatten(-1, (G, 128)), vc[:, 0, :G * 128].unflatten(-1, (G, 128))      # the leading columns of the pool's rows
             if ops.tc_attention_ok(q, k4, v4, fb.page_size):
@@ -172,8 +174,10 @@ class GatedAttention(nn.Module):
                                         causal=True, window=self.window, logit_cap=self.softcap, num_splits=fb.num_splits if dec else 1,
                                         workspace=fb.attn_workspace if dec else None, lse=lse, slopes=self.r1, log_rates=self.r2, keep_first=self.keep_first)
                 if turn:             # the sink's share, the back-rotation and the end of the head padding in one pass
-                    o = ops.rotate_heads(o, fb.positions, self.v_inv_freq, Dv, self.v_interleaved, True, lse, self.sinks,
-                                         out if gate is None and self.out_scale == 1.0 and out is not None and out.is_contiguous() else None).view(T, H, Dv)
+                    o = ops.rotate_heads(o, fb.positions, self.v_inv_freq, Dv, self.v_interleaved, True, lse, self.sinks, direct)
+                    if direct is not None:
+                        return o
+                    o = o.view(T, H, Dv)
                 elif lse is not None:
                     o = ops.attention_sink_gate(o, lse, self.sinks, Dv)
                 if gate is None:
@@ -184,8 +188,9 @@ class GatedAttention(nn.Module):
                                  1.0 if turn else self.out_scale, None if turn else out)
         if not turn:
             return o.reshape(T, H * Dv)
-        o = ops.rotate_heads(o.reshape(T, H, Dv), fb.positions, self.v_inv_freq, Dv, self.v_interleaved, True, None, None,
-                             out if gate is None and self.out_scale == 1.0 and out is not None and out.is_contiguous() else None)
+        o = ops.rotate_heads(o.reshape(T, H, Dv), fb.positions, self.v_inv_freq, Dv, self.v_interleaved, True, None, None, direct)
+        if direct is not None:
+            return o
         if gate is None:
             return self._plain(o.view(T, H, Dv), Dv, out)
         return ops.sigmoid_gate(o.view(T, H, Dv), gate, Dv, self.out_scale, out)
@@ -193,8 +198,6 @@ class GatedAttention(nn.Module):
     def _plain(self, o: torch.Tensor, Dv: int, out: Optional[torch.Tensor]) -> torch.Tensor:
         """ungated heads [T, H, >= Dv] -> [T, H * Dv] (times ``out_scale``), into ``out`` when given"""
         T, H = o.shape[0], o.shape[1]
-        if out is not None and o.shape[2] == Dv and o.data_ptr() == out.data_ptr():
-            return out
         y = o[:, :, :Dv].reshape(T, H * Dv)
         if self.out_scale != 1.0:
             y = (y.float() * self.out_scale).to(o.dtype)
